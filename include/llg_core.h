@@ -1,0 +1,160 @@
+/* libllg_core: C ABI of the B200 (sm_100a) low-latency GEMM core.
+ *
+ * Plain pointers, sizes and strides only - no torch types. Every pointer is a DEVICE pointer unless a comment
+ * says otherwise. The caller owns all buffers; the library allocates nothing, keeps no pointer after a call
+ * returns, and launches on the CUDA stream it is given (a cudaStream_t passed as void*; NULL = default stream) on
+ * the device that is current in the calling thread. Launch descriptors (including TMA tensor maps) are passed to
+ * the kernels by value, so calls are legal during CUDA-graph capture.
+ *
+ * Return value of the int functions: 0 on success, a negative LLG_E_* code on failure; llg_last_error() then
+ * returns a message prefixed "lowlat_gemm: " (thread-local, valid until the next failing call of that thread).
+ *
+ * Each entry point states which interface of the reference (Cerynitius/sm120-lowlat-gemm) it stands in for.
+ */
+#ifndef LLG_CORE_H_
+#define LLG_CORE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLG_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define LLG_API __attribute__((visibility("default")))
+#else
+#define LLG_API
+#endif
+
+enum {
+  LLG_OK = 0,
+  LLG_E_INVALID = -1,   /* argument validation failed (reference: TORCH_CHECK in csrc/ops.cpp) */
+  LLG_E_CONFIG = -2,    /* tile config cannot be launched for this kind (reference: csrc/ops.cpp:294-298) */
+  LLG_E_CUDA = -3,      /* a CUDA runtime / driver call failed */
+  LLG_E_UNAVAILABLE = -4 /* the library was built without this kernel */
+};
+
+/* Precision kinds; ids equal the reference's enum TcKind (csrc/tc_params.h:10-21) and KINDS table
+ * (lowlat_gemm/__init__.py:64-74). */
+enum {
+  LLG_KIND_BF16 = 0,
+  LLG_KIND_F16 = 1,
+  LLG_KIND_FP8 = 2,
+  LLG_KIND_INT8 = 3,
+  LLG_KIND_NVFP4 = 4,
+  LLG_KIND_W8A16_BF16 = 5,
+  LLG_KIND_W8A16_F16 = 6,
+  LLG_KIND_W4A16_BF16 = 7,
+  LLG_KIND_W4A16_F16 = 8,
+  LLG_KIND_COUNT = 9
+};
+
+/* Element types of 16/32-bit tensors; values equal the reference's enum DType (csrc/tc_params.h:23). */
+enum { LLG_DT_NONE = 0, LLG_DT_BF16 = 1, LLG_DT_F16 = 2, LLG_DT_F32 = 3 };
+
+/* Quantizer modes; values equal the reference's enum QuantMode (csrc/quant.h:9-14). */
+enum { LLG_QUANT_FP8_STATIC = 0, LLG_QUANT_FP8_PER_TOKEN = 1, LLG_QUANT_INT8_PER_TOKEN = 2, LLG_QUANT_NVFP4 = 3 };
+
+#define LLG_NUM_CFGS 10
+#define LLG_MAX_STAGES 16
+#define LLG_SKINNY_MAX_TOKENS 16
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Skinny streaming GEMV: y[M,N] = x[M,K] @ w[N,K]^T for bf16/f16 with M <= 16, fp32 accumulation in an order that
+ * depends on (K, lanes_per_row, ksplit) only, so a row of the result is bit-identical for every M and tile.
+ * Stands in for torch.ops.lowlat_gemm.skinny_out (reference csrc/ops.cpp:59-129, 381-385; launch descriptor
+ * csrc/params.h:10-34; kernel csrc/gemv.cuh:74-234). */
+typedef struct llg_skinny_args {
+  const void* x;  int64_t ldx;   /* [M,K], row stride in elements, 16-byte aligned, ldx % 8 == 0 */
+  const void* w;  int64_t ldw;   /* [N,K], same element type as x */
+  void* y;        int64_t ldy;   /* [M,N], element type of x, or fp32 when out_fp32 */
+  int32_t M, N, K;               /* 1 <= M <= 16, K % 8 == 0 */
+  int32_t f16;                   /* 0: bf16, 1: f16 */
+  int32_t out_fp32;
+  int32_t rows, unroll, lanes_per_row, warps, ksplit; /* tile: (rows,unroll) in {(1,2),(1,4),(1,8),(2,2),(2,4),(4,2)} */
+  int32_t cluster;               /* split-K reduced through cluster shared memory (ksplit <= 8) */
+  float* ws;      int64_t ws_elems;        /* split-K partials, >= ksplit*M*N floats (workspace mode) */
+  int32_t* counters; int64_t counters_elems; /* >= ceil(N / rows_per_block) ints, zero between launches */
+  const void* prefetch; int64_t prefetch_bytes; /* optional L2 prefetch range (16-byte aligned), NULL = none */
+} llg_skinny_args;
+
+LLG_API int llg_skinny(const llg_skinny_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Tensor-core GEMM (tcgen05): C[p,q] = sum_k A[p,k] B[q,k], then
+ *   v = ((acc * alpha * (*alpha_ptr)) * row_scale[p]) * col_scale[q]   (fp32, each product rounded)
+ *   v = v + bias[p or q]                                               (rounded add, no fused multiply-add)
+ * stored as y[q,p] when swap else y[p,q]. INT8 accumulates in int32 (exact) and converts once.
+ * Stands in for torch.ops.lowlat_gemm.tc_gemm (reference csrc/ops.cpp:201-300, 393-401; descriptor
+ * csrc/tc_params.h:28-60; kernel csrc/tc_gemm.cuh:179-501). */
+typedef struct llg_tc_args {
+  int32_t kind;                  /* LLG_KIND_* */
+  int32_t cfg, stages, ksplit;   /* tile config [0, LLG_NUM_CFGS), pipeline depth (clamped), K partitions [1,64] */
+  int32_t cluster;               /* split-K through cluster shared memory (ksplit <= 8) instead of the workspace */
+  int32_t swap;                  /* y stored transposed: A is the weight */
+  const void* a;  int64_t a_rows, a_row_bytes, lda_bytes;  /* A [P, K] as bytes, rows 16-byte aligned */
+  const void* b;  int64_t b_rows, b_row_bytes, ldb_bytes;  /* B [Q, K] */
+  const void* a_sf; int64_t lda_sf;  /* block scales of A: [P, K/16] e4m3 bytes, row stride % 4 == 0 (NVFP4, W4A16) */
+  const void* b_sf; int64_t ldb_sf;  /* block scales of B (NVFP4) */
+  const float* row_scale; int32_t row_scale_len;  /* 0 none, 1 scalar, else P */
+  const float* col_scale; int32_t col_scale_len;  /* 0 none, 1 scalar, else Q */
+  const void* bias; int32_t bias_dtype; int32_t bias_on_p;  /* LLG_DT_*; indexed by p or by q */
+  const float* alpha_ptr; float alpha;
+  void* y; int64_t ldy; int32_t out_dtype;        /* row stride in elements; LLG_DT_* */
+  void* ws; int64_t ws_elems;                     /* split-K partials (4-byte), >= ksplit*P*Q */
+  int32_t* counters; int64_t counters_elems;      /* >= number of output tiles, zero between launches */
+  const void* prefetch; int64_t prefetch_bytes;
+} llg_tc_args;
+
+LLG_API int llg_tc_gemm(const llg_tc_args* args, void* stream);
+
+/* (BP, BQ, threads, shared bytes per pipeline stage) of a tile config; stands in for
+ * torch.ops.lowlat_gemm.tc_info (reference csrc/ops.cpp:412-416, csrc/tc_info.cu:8-61). Returns 0 or LLG_E_INVALID. */
+LLG_API int llg_tc_info(int32_t kind, int32_t cfg, int32_t out[4]);
+
+/* Dynamic shared memory a CTA may use for pipeline stages on this build (bytes); the Python planner divides it by
+ * the stage size where the reference hard-codes 99 KB (lowlat_gemm/__init__.py:208, csrc/tc_gemm.cuh:141). */
+LLG_API int32_t llg_smem_budget(void);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Activation quantizers, one call per [M,K] matrix. Stands in for torch.ops.lowlat_gemm.quant (reference
+ * csrc/ops.cpp:305-367; descriptor csrc/quant.h:16-29; kernels csrc/quant.cu:43-114). Bit-exact with them. */
+typedef struct llg_quant_args {
+  int32_t mode;          /* LLG_QUANT_* */
+  int32_t in_dtype;      /* LLG_DT_BF16 / F16 / F32 */
+  const void* x; int64_t ldx;   /* [M,K], row stride in elements */
+  void* q; int64_t ldq;         /* [M,K] bytes, or [M,K/2] packed fp4 (low nibble = even element); stride in bytes */
+  void* sf_out; int64_t ldsf;   /* nvfp4: [M,K/16] e4m3 bytes */
+  const float* scale_in;        /* fp8 static: the scale; nvfp4: the global scale g (1 float, device) */
+  float* scale_out;             /* per-token modes: [M] */
+  float min_scale;
+  int32_t M, K;
+} llg_quant_args;
+
+LLG_API int llg_quant(const llg_quant_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Process-wide programmatic-dependent-launch switch; stands in for torch.ops.lowlat_gemm.set_pdl / pdl_enabled
+ * (reference csrc/ops.cpp:409-410, csrc/tc_info.cu:67-70). */
+LLG_API void llg_set_pdl(int32_t on);
+LLG_API int32_t llg_pdl_enabled(void);
+
+/* Host-buffer convenience used for end-to-end timing: copies x (HOST, pinned or pageable) to x_dev, runs the GEMM
+ * described by `args` (whose activation operand must already point at x_dev), copies y back to y_host, all on
+ * `stream`, without synchronising. No counterpart in the reference (its callers hold device tensors). */
+LLG_API int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* x_dev, int64_t x_bytes, void* y_host,
+                     int64_t y_bytes, void* stream);
+
+/* Reads and clears the device status word of the current device (synchronises the device). 0 = no kernel ever gave
+ * up a bounded wait; otherwise the code of the first wait that expired. No counterpart in the reference. */
+LLG_API int llg_device_status(uint32_t* status);
+
+LLG_API const char* llg_last_error(void);
+LLG_API int32_t llg_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLG_CORE_H_ */

@@ -1,0 +1,412 @@
+// C ABI of libllg_core (declared in include/llg_core.h): argument validation, TMA tensor maps, kernel dispatch.
+//
+// Validation rules and messages follow the reference's binding layer csrc/ops.cpp (skinny_run 59-129,
+// tc_gemm_impl 201-300, quant_impl 305-367); checks that need tensor metadata (device, dtype object, contiguity)
+// are done by the Python wrapper, everything that can be decided from pointers, sizes and strides is decided here.
+#include <cudaTypedefs.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "llg_internal.h"
+
+namespace llg {
+
+int tc_stage_bytes_f16(int cfg);
+int tc_stage_bytes_f8(int cfg);
+int tc_stage_bytes_i8(int cfg);
+int tc_stage_bytes_nvf4(int cfg);
+int tc_stage_bytes_w8a16(int cfg);
+int tc_stage_bytes_w4a16(int cfg);
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  int n = snprintf(g_err, sizeof(g_err), "lowlat_gemm: ");
+  vsnprintf(g_err + n, sizeof(g_err) - n, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(const char* what, cudaError_t e) {
+  return fail(LLG_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool aligned(const void* p, uintptr_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
+
+std::atomic<bool> g_pdl{false};
+
+__device__ unsigned int g_status_word = 0;
+
+struct KindSpec {
+  int a_bits, b_bits;
+  bool a_sf, b_sf;
+  int k_align;
+};
+
+bool kind_spec(int kind, KindSpec* k) {
+  switch (kind) {
+    case LLG_KIND_BF16:
+    case LLG_KIND_F16: *k = {16, 16, false, false, 8}; return true;
+    case LLG_KIND_FP8:
+    case LLG_KIND_INT8: *k = {8, 8, false, false, 16}; return true;
+    case LLG_KIND_NVFP4: *k = {4, 4, true, true, 64}; return true;
+    case LLG_KIND_W8A16_BF16:
+    case LLG_KIND_W8A16_F16: *k = {8, 16, false, false, 16}; return true;
+    case LLG_KIND_W4A16_BF16:
+    case LLG_KIND_W4A16_F16: *k = {4, 16, true, false, 64}; return true;
+    default: return false;
+  }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// Byte-typed 2-D map over a row-major matrix: dim0 = bytes of one row, dim1 = rows; box = 128 bytes x box_rows with the
+// 128-byte swizzle the MMA descriptors expect; out-of-range parts of a box read as zero.
+bool make_map(CUtensorMap* m, const void* ptr, int64_t row_bytes, int64_t rows, int64_t ld_bytes, int box_rows,
+              bool streamed) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+  cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        streamed ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool pdl_on() { return g_pdl.load(std::memory_order_relaxed); }
+
+int sm_count() {
+  static int counts[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (counts[dev] == 0) cudaDeviceGetAttribute(&counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  return counts[dev];
+}
+
+unsigned int* status_word_device_ptr() {
+  static unsigned int* ptrs[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<unsigned int*>(p);
+  }
+  return ptrs[dev];
+}
+
+TcTile tc_tile_of(int cfg) {
+  static const int bq[5] = {16, 32, 64, 128, 256};
+  if (cfg < 0 || cfg >= LLG_NUM_CFGS) return {0, 0};
+  return {bq[cfg % 5], 1 + cfg / 5};
+}
+
+int tc_family_of(int kind) {
+  switch (kind) {
+    case LLG_KIND_BF16:
+    case LLG_KIND_F16: return FAM_F16;
+    case LLG_KIND_FP8: return FAM_F8;
+    case LLG_KIND_INT8: return FAM_I8;
+    case LLG_KIND_NVFP4: return FAM_NVF4;
+    case LLG_KIND_W8A16_BF16:
+    case LLG_KIND_W8A16_F16: return FAM_W8A16;
+    case LLG_KIND_W4A16_BF16:
+    case LLG_KIND_W4A16_F16: return FAM_W4A16;
+    default: return -1;
+  }
+}
+
+int tc_stage_bytes_of(int kind, int cfg) {
+  switch (tc_family_of(kind)) {
+    case FAM_F16: return tc_stage_bytes_f16(cfg);
+    case FAM_F8: return tc_stage_bytes_f8(cfg);
+    case FAM_I8: return tc_stage_bytes_i8(cfg);
+    case FAM_NVF4: return tc_stage_bytes_nvf4(cfg);
+    case FAM_W8A16: return tc_stage_bytes_w8a16(cfg);
+    case FAM_W4A16: return tc_stage_bytes_w4a16(cfg);
+    default: return 0;
+  }
+}
+
+}  // namespace llg
+
+using namespace llg;
+
+extern "C" {
+
+const char* llg_last_error(void) { return g_err; }
+int32_t llg_abi_version(void) { return LLG_ABI_VERSION; }
+void llg_set_pdl(int32_t on) { g_pdl.store(on != 0, std::memory_order_relaxed); }
+int32_t llg_pdl_enabled(void) { return g_pdl.load(std::memory_order_relaxed) ? 1 : 0; }
+int32_t llg_smem_budget(void) { return kSmemBudget; }
+
+int llg_device_status(uint32_t* status) {
+  unsigned int* dptr = status_word_device_ptr();
+  if (!dptr) return fail(LLG_E_CUDA, "no device status word");
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail("device synchronize", e);
+  unsigned int v = 0;
+  e = cudaMemcpy(&v, dptr, sizeof(v), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail("status read", e);
+  if (v != 0) {
+    const unsigned int zero = 0;
+    cudaMemcpy(dptr, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+  }
+  if (status) *status = v;
+  return LLG_OK;
+}
+
+int llg_tc_info(int32_t kind, int32_t cfg, int32_t out[4]) {
+  const TcTile t = tc_tile_of(cfg);
+  if (t.bq == 0 || tc_family_of(kind) < 0) return fail(LLG_E_INVALID, "unknown kind %d or cfg %d", kind, cfg);
+  out[0] = 128;
+  out[1] = t.bq;
+  out[2] = kTcThreads;
+  out[3] = tc_stage_bytes_of(kind, cfg);
+  return LLG_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+
+int llg_skinny(const llg_skinny_args* a, void* stream) {
+  if (!a) return fail(LLG_E_INVALID, "null arguments");
+  const int ru = a->rows * 16 + a->unroll;
+  if (!(ru == 0x12 || ru == 0x14 || ru == 0x18 || ru == 0x22 || ru == 0x24 || ru == 0x42))
+    return fail(LLG_E_INVALID, "unsupported (rows, unroll) = (%d, %d); supported: (1,2) (1,4) (1,8) (2,2) (2,4) (4,2)",
+                a->rows, a->unroll);
+  if (!(a->lanes_per_row == 8 || a->lanes_per_row == 16 || a->lanes_per_row == 32))
+    return fail(LLG_E_INVALID, "lanes_per_row must be 8, 16 or 32, got %d", a->lanes_per_row);
+  if (a->warps < 1 || a->warps > 8) return fail(LLG_E_INVALID, "warps must be in [1, 8], got %d", a->warps);
+  if (a->ksplit < 1 || a->ksplit > 64) return fail(LLG_E_INVALID, "ksplit must be in [1, 64], got %d", a->ksplit);
+  if (!a->x || !a->w || !a->y) return fail(LLG_E_INVALID, "x, w, y must be device pointers");
+  if (a->M < 1 || a->M > LLG_SKINNY_MAX_TOKENS) return fail(LLG_E_INVALID, "skinny: M must be in [1, 16], got %d", a->M);
+  if (a->K <= 0 || a->K % 8) return fail(LLG_E_INVALID, "skinny: K must be a positive multiple of 8, got %d", a->K);
+  if (a->N < 1) return fail(LLG_E_INVALID, "N or K too large");
+  if (a->ldx % 8 || a->ldw % 8) return fail(LLG_E_INVALID, "x and w row strides must be multiples of 8 elements");
+  if (!aligned(a->x, 16) || !aligned(a->w, 16)) return fail(LLG_E_INVALID, "x and w must be 16-byte aligned");
+  const int64_t rows_cta = (int64_t)a->warps * (32 / a->lanes_per_row) * a->rows;
+  const int64_t columns = (a->N + rows_cta - 1) / rows_cta;
+  const bool cluster = a->cluster && a->ksplit > 1;
+  if (cluster && a->ksplit > 8) return fail(LLG_E_INVALID, "cluster split-K supports ksplit <= 8, got %d", a->ksplit);
+  if (a->ksplit > 1 && !cluster) {
+    if (!a->ws || !a->counters) return fail(LLG_E_INVALID, "workspace must be contiguous float32, counters contiguous int32");
+    if (a->ws_elems < (int64_t)a->ksplit * a->M * a->N)
+      return fail(LLG_E_INVALID, "workspace has %lld floats, needs %lld", (long long)a->ws_elems,
+                  (long long)a->ksplit * a->M * a->N);
+    if (a->counters_elems < columns)
+      return fail(LLG_E_INVALID, "counters has %lld, needs %lld", (long long)a->counters_elems, (long long)columns);
+  }
+  if (a->prefetch && !aligned(a->prefetch, 16))
+    return fail(LLG_E_INVALID, "prefetch tensor must be contiguous and 16-byte aligned");
+
+  SkinnyDev p{};
+  p.x = a->x; p.w = a->w; p.y = a->y;
+  p.ldx = a->ldx; p.ldw = a->ldw; p.ldy = a->ldy;
+  p.M = a->M; p.N = a->N; p.K = a->K; p.ksplit = a->ksplit;
+  p.ws = a->ksplit > 1 && !cluster ? a->ws : nullptr;
+  p.counters = a->ksplit > 1 && !cluster ? reinterpret_cast<unsigned*>(a->counters) : nullptr;
+  p.pf = a->prefetch; p.pf_bytes = a->prefetch ? a->prefetch_bytes : 0;
+  p.out_fp32 = a->out_fp32 != 0;
+  p.cluster = cluster;
+  const bool pdl = pdl_on();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  switch (a->lanes_per_row) {
+    case 8: e = skinny_launch_l8(p, a->rows, a->unroll, a->warps, a->f16 != 0, pdl, s); break;
+    case 16: e = skinny_launch_l16(p, a->rows, a->unroll, a->warps, a->f16 != 0, pdl, s); break;
+    default: e = skinny_launch_l32(p, a->rows, a->unroll, a->warps, a->f16 != 0, pdl, s); break;
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LLG_E_CUDA, "skinny: no kernel for M=%d rows=%d unroll=%d (%s)", a->M, a->rows, a->unroll, cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+
+static int check_operand(const void* ptr, int64_t ld_bytes, const char* name) {
+  if (!ptr) return fail(LLG_E_INVALID, "operands must be on CUDA");
+  if (ld_bytes % 16) return fail(LLG_E_INVALID, "%s row stride must be a multiple of 16 bytes", name);
+  if (!aligned(ptr, 16)) return fail(LLG_E_INVALID, "%s must be 16-byte aligned", name);
+  return 0;
+}
+
+int llg_tc_gemm(const llg_tc_args* a, void* stream) {
+  if (!a) return fail(LLG_E_INVALID, "null arguments");
+  KindSpec ks;
+  if (!kind_spec(a->kind, &ks)) return fail(LLG_E_INVALID, "unknown kind %d", a->kind);
+  if (a->cfg < 0 || a->cfg >= LLG_NUM_CFGS) return fail(LLG_E_INVALID, "cfg must be in [0, %d), got %d", LLG_NUM_CFGS, a->cfg);
+  if (a->ksplit < 1 || a->ksplit > 64) return fail(LLG_E_INVALID, "ksplit must be in [1, 64], got %d", a->ksplit);
+  if (int r = check_operand(a->a, a->lda_bytes, "a")) return r;
+  if (int r = check_operand(a->b, a->ldb_bytes, "b")) return r;
+  const int64_t P = a->a_rows, Q = a->b_rows;
+  const int64_t K = a->a_row_bytes * 8 / ks.a_bits, Kb = a->b_row_bytes * 8 / ks.b_bits;
+  if (K != Kb) return fail(LLG_E_INVALID, "a holds K=%lld but b holds K=%lld", (long long)K, (long long)Kb);
+  if (K <= 0 || K % ks.k_align)
+    return fail(LLG_E_INVALID, "K must be a positive multiple of %d for this kind, got %lld", ks.k_align, (long long)K);
+  if (P < 1 || Q < 1 || P > INT32_MAX || Q > INT32_MAX || K > INT32_MAX) return fail(LLG_E_INVALID, "empty or too large problem");
+  if (!a->y) return fail(LLG_E_INVALID, "y must be 2-D with unit last stride");
+  if (a->out_dtype < LLG_DT_BF16 || a->out_dtype > LLG_DT_F32) return fail(LLG_E_INVALID, "y must be bfloat16, float16 or float32");
+  const bool mixed = a->kind >= LLG_KIND_W8A16_BF16;
+  if (mixed && !a->swap) return fail(LLG_E_INVALID, "mixed-precision kinds need the weight as operand a (swap)");
+
+  TcDev p{};
+  if (ks.a_sf) {
+    if (!a->a_sf) return fail(LLG_E_INVALID, "this kind needs block scales for a");
+    if (a->lda_sf % 4 || !aligned(a->a_sf, 4))
+      return fail(LLG_E_INVALID, "a_sf needs unit column stride, a row stride that is a multiple of 4 and 4-byte alignment");
+    p.a_sf = static_cast<const unsigned char*>(a->a_sf);
+    p.lda_sf = a->lda_sf;
+  }
+  if (ks.b_sf) {
+    if (!a->b_sf) return fail(LLG_E_INVALID, "this kind needs block scales for b");
+    if (a->ldb_sf % 4 || !aligned(a->b_sf, 4))
+      return fail(LLG_E_INVALID, "b_sf needs unit column stride, a row stride that is a multiple of 4 and 4-byte alignment");
+    p.b_sf = static_cast<const unsigned char*>(a->b_sf);
+    p.ldb_sf = a->ldb_sf;
+  }
+  if (a->row_scale_len != 0 && a->row_scale_len != 1 && a->row_scale_len != P)
+    return fail(LLG_E_INVALID, "row_scale must have 1 or %lld elements, got %d", (long long)P, a->row_scale_len);
+  if (a->col_scale_len != 0 && a->col_scale_len != 1 && a->col_scale_len != Q)
+    return fail(LLG_E_INVALID, "col_scale must have 1 or %lld elements, got %d", (long long)Q, a->col_scale_len);
+  if ((a->row_scale_len && !a->row_scale) || (a->col_scale_len && !a->col_scale))
+    return fail(LLG_E_INVALID, "scale vector length given without a pointer");
+  if (a->bias) {
+    if (a->bias_dtype < LLG_DT_BF16 || a->bias_dtype > LLG_DT_F32)
+      return fail(LLG_E_INVALID, "bias must be a contiguous bf16/f16/f32 vector of %lld elements", (long long)(a->bias_on_p ? P : Q));
+  }
+  const bool cluster = a->cluster && a->ksplit > 1;
+  if (cluster && a->ksplit > 8) return fail(LLG_E_INVALID, "cluster split-K supports ksplit <= 8, got %d", a->ksplit);
+  const TcTile tile = tc_tile_of(a->cfg);
+  if (a->ksplit > 1 && !cluster) {
+    const int64_t tiles = ((P + 127) / 128) * ((Q + tile.bq - 1) / tile.bq);
+    if (!a->ws || !a->counters) return fail(LLG_E_INVALID, "workspace must be a contiguous 4-byte tensor, counters contiguous int32");
+    if (a->ws_elems < (int64_t)a->ksplit * P * Q)
+      return fail(LLG_E_INVALID, "workspace has %lld elements, needs %lld", (long long)a->ws_elems, (long long)a->ksplit * P * Q);
+    if (a->counters_elems < tiles)
+      return fail(LLG_E_INVALID, "counters has %lld, needs %lld", (long long)a->counters_elems, (long long)tiles);
+    p.ws = a->ws;
+    p.counters = reinterpret_cast<unsigned*>(a->counters);
+  }
+  if (a->prefetch && !aligned(a->prefetch, 16))
+    return fail(LLG_E_INVALID, "prefetch tensor must be contiguous and 16-byte aligned");
+  if (tc_stage_bytes_of(a->kind, a->cfg) == 0)
+    return fail(LLG_E_CONFIG, "config %d cannot be launched for this kind: stage does not fit shared memory", a->cfg);
+
+  p.row_scale = a->row_scale; p.row_scale_len = a->row_scale_len;
+  p.col_scale = a->col_scale; p.col_scale_len = a->col_scale_len;
+  p.bias = a->bias; p.bias_dtype = a->bias ? a->bias_dtype : LLG_DT_NONE; p.bias_on_p = a->bias_on_p != 0;
+  p.alpha_ptr = a->alpha_ptr; p.alpha = a->alpha;
+  p.y = a->y; p.ldy = a->ldy; p.out_dtype = a->out_dtype;
+  p.P = (int)P; p.Q = (int)Q; p.K = (int)K;
+  p.k_atoms = (int)((a->a_row_bytes + 127) / 128);
+  p.ksplit = a->ksplit; p.stages = a->stages;
+  p.swap = a->swap != 0; p.cluster = cluster; p.a_is_weight = a->swap != 0;
+  p.pf = a->prefetch; p.pf_bytes = a->prefetch ? a->prefetch_bytes : 0;
+  p.status = status_word_device_ptr();
+  if (!p.status) return fail(LLG_E_CUDA, "no device status word");
+  const uint32_t bq = (uint32_t)tile.bq;
+  switch (a->kind) {
+    case LLG_KIND_BF16: case LLG_KIND_W8A16_BF16: case LLG_KIND_W4A16_BF16:
+      p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((bq >> 3) << 17) | ((128u >> 4) << 24); p.bf16_act = 1; break;
+    case LLG_KIND_F16: case LLG_KIND_W8A16_F16: case LLG_KIND_W4A16_F16:
+      p.idesc = (1u << 4) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;
+    case LLG_KIND_FP8: p.idesc = (1u << 4) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;          // e4m3 = format 0
+    case LLG_KIND_INT8: p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;
+    case LLG_KIND_NVFP4: p.idesc = (1u << 7) | (1u << 10) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;  // e2m1, ue4m3 scales
+  }
+
+  CUtensorMap ta, tb;
+  if (!make_map(&ta, a->a, a->a_row_bytes, P, a->lda_bytes, 128, p.a_is_weight) ||
+      !make_map(&tb, a->b, a->b_row_bytes, Q, a->ldb_bytes, tile.bq, !p.a_is_weight))
+    return fail(LLG_E_CUDA, "cuTensorMapEncodeTiled failed (operand layout not expressible as a TMA map)");
+
+  const bool pdl = pdl_on();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  switch (tc_family_of(a->kind)) {
+    case FAM_F16: e = tc_launch_f16(ta, tb, p, a->cfg, pdl, s); break;
+    case FAM_F8: e = tc_launch_f8(ta, tb, p, a->cfg, pdl, s); break;
+    case FAM_I8: e = tc_launch_i8(ta, tb, p, a->cfg, pdl, s); break;
+    case FAM_NVF4: e = tc_launch_nvf4(ta, tb, p, a->cfg, pdl, s); break;
+    case FAM_W8A16: e = tc_launch_w8a16(ta, tb, p, a->cfg, pdl, s); break;
+    default: e = tc_launch_w4a16(ta, tb, p, a->cfg, pdl, s); break;
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(e == cudaErrorInvalidConfiguration ? LLG_E_CONFIG : LLG_E_CUDA,
+                "config %d cannot be launched for this kind: %s", a->cfg, cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
+int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* x_dev, int64_t x_bytes, void* y_host,
+                     int64_t y_bytes, void* stream) {
+  if (!args || !x_host || !x_dev || !y_host) return fail(LLG_E_INVALID, "null arguments");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(x_dev, x_host, (size_t)x_bytes, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return cuda_fail("host to device copy", e);
+  if (int r = llg_tc_gemm(args, stream)) return r;
+  e = cudaMemcpyAsync(y_host, args->y, (size_t)y_bytes, cudaMemcpyDeviceToHost, s);
+  if (e != cudaSuccess) return cuda_fail("device to host copy", e);
+  return LLG_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+
+int llg_quant(const llg_quant_args* a, void* stream) {
+  if (!a) return fail(LLG_E_INVALID, "null arguments");
+  if (a->in_dtype < LLG_DT_BF16 || a->in_dtype > LLG_DT_F32) return fail(LLG_E_INVALID, "quant: x must be bf16, f16 or f32");
+  if (a->M < 0 || a->K < 0) return fail(LLG_E_INVALID, "quant: x must be a 2-D CUDA tensor with unit last stride");
+  switch (a->mode) {
+    case LLG_QUANT_FP8_STATIC:
+      if (!a->scale_in) return fail(LLG_E_INVALID, "quant: this mode needs scale_in float32[1]");
+      break;
+    case LLG_QUANT_FP8_PER_TOKEN:
+    case LLG_QUANT_INT8_PER_TOKEN:
+      if (!a->scale_out) return fail(LLG_E_INVALID, "quant: per-token modes need scale_out float32[M]");
+      break;
+    case LLG_QUANT_NVFP4:
+      if (a->K % 16) return fail(LLG_E_INVALID, "quant: nvfp4 needs K %% 16 == 0");
+      if (a->ldq % 8 || !aligned(a->q, 8)) return fail(LLG_E_INVALID, "quant: q must be [M, K/2] bytes with 8-byte aligned rows");
+      if (!a->sf_out) return fail(LLG_E_INVALID, "quant: nvfp4 needs sf [M, K/16] bytes");
+      if (!a->scale_in) return fail(LLG_E_INVALID, "quant: this mode needs scale_in float32[1]");
+      break;
+    default: return fail(LLG_E_INVALID, "quant: unknown mode %d", a->mode);
+  }
+  if (a->M == 0 || a->K == 0) return LLG_OK;
+  if (!a->x || !a->q) return fail(LLG_E_INVALID, "quant: q must be a 2-D 1-byte tensor with M rows");
+  const cudaError_t e = quant_launch(*a, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LLG_E_CUDA, "quant: launch failed (%s)", cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,130 @@
+// Internal launch interfaces between the C-ABI layer (api.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/llg_core.h"
+
+namespace llg {
+
+// ---- status word ------------------------------------------------------------------------------------------------
+// One word per device, set by a kernel whose bounded wait expired (first code wins). Codes:
+enum : uint32_t {
+  ST_OK = 0,
+  ST_PRODUCER_EMPTY_WAIT = 1,  // TMA producer waited for a free pipeline slot
+  ST_MMA_FULL_WAIT = 2,        // MMA issuer waited for operands
+  ST_EPILOGUE_WAIT = 3,        // epilogue waited for the accumulator
+  ST_CONVERT_WAIT = 4,         // converter / scale warps waited for a buffer
+  ST_DRAIN_WAIT = 5,           // producer waited for its own copies while leaving early
+};
+unsigned int* status_word_device_ptr();  // device address of the status word of the current device (cached)
+
+// ---- process-wide switches / caches --------------------------------------------------------------------------
+bool pdl_on();
+int sm_count();
+
+// Launch with optional PDL attribute and cluster shape.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             bool pdl, dim3 cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster.x * cluster.y * cluster.z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster.x;
+    attr[n].val.clusterDim.y = cluster.y;
+    attr[n].val.clusterDim.z = cluster.z;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// ---- skinny GEMV -------------------------------------------------------------------------------------------------
+struct SkinnyDev {
+  const void* x;
+  const void* w;
+  void* y;
+  int64_t ldx, ldw, ldy;
+  int M, N, K, ksplit;
+  float* ws;
+  unsigned* counters;
+  const void* pf;
+  int64_t pf_bytes;
+  unsigned char out_fp32, cluster, pdl_early;
+};
+// One translation unit per lanes-per-row; returns cudaErrorInvalidValue for an unsupported tile.
+cudaError_t skinny_launch_l8(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
+cudaError_t skinny_launch_l16(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
+cudaError_t skinny_launch_l32(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
+
+// ---- quantizers --------------------------------------------------------------------------------------------------
+cudaError_t quant_launch(const llg_quant_args& a, cudaStream_t s);
+
+// ---- tensor-core GEMM --------------------------------------------------------------------------------------------
+// Kernel families (one template instantiation set each).
+enum TcFamily : int { FAM_F16 = 0, FAM_F8 = 1, FAM_I8 = 2, FAM_NVF4 = 3, FAM_W8A16 = 4, FAM_W4A16 = 5, FAM_COUNT = 6 };
+
+struct TcDev {
+  // epilogue
+  const float* row_scale;
+  const float* col_scale;
+  const void* bias;
+  const float* alpha_ptr;
+  void* y;
+  int64_t ldy;
+  float alpha;
+  int row_scale_len, col_scale_len;
+  int bias_dtype, out_dtype;
+  // block scales (row-major [rows, K/16] bytes)
+  const unsigned char* a_sf;
+  const unsigned char* b_sf;
+  int64_t lda_sf, ldb_sf;
+  // problem
+  int P, Q, K;          // K in elements
+  int k_atoms;          // ceil(K bytes of the streamed (narrower) operand per row / 128)
+  int ksplit, stages;
+  uint32_t idesc;
+  // split-K
+  void* ws;
+  unsigned* counters;
+  // misc
+  const void* pf;
+  int64_t pf_bytes;
+  unsigned* status;
+  unsigned char swap, bias_on_p, cluster, pdl_early, a_is_weight, bf16_act;
+};
+
+struct TcTile {
+  int bq;      // 16, 32, 64, 128, 256 (BP is always 128)
+  int atoms;   // 128-byte K atoms of the A operand per pipeline stage (1 or 2)
+};
+TcTile tc_tile_of(int cfg);
+int tc_family_of(int kind);
+// bytes per stage of (family, cfg); 0 if invalid
+int tc_stage_bytes_of(int kind, int cfg);
+constexpr int kTcThreads = 192;
+constexpr int kSmemBudget = 227 * 1024 - 2048;  // dynamic shared memory for stages; the rest holds barriers and slack
+
+// Defined per family in umma_<family>.cu.
+cudaError_t tc_launch_f16(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_f8(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_i8(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_nvf4(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_w8a16(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_w4a16(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+
+}  // namespace llg

@@ -1,0 +1,672 @@
+// Tensor-core GEMM for sm_100a: C[p,q] = sum_k A[p,k] B[q,k], both operands K-contiguous.
+//
+// One CTA computes a 128 x BQ output tile for one K partition:
+//   warp 0      TMA producer: 128-byte-swizzled tiles of A and B into a ring of shared-memory stages
+//   warp 1      allocates tensor memory and issues tcgen05.mma (accumulator lives in tensor memory)
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, scale / bias / convert / store, split-K reduction;
+//               for the mixed kinds (W8A16, W4A16) they first widen the weight tile exactly into tensor memory
+//               (the MMA then takes A from tensor memory); for NVFP4 they feed the block scales
+// The host maps (activation, weight) onto (A, B): with few tokens the weight is A ("swap": its rows fill the 128
+// MMA rows, the tokens sit on the narrow N side and y is stored transposed).
+//
+// Reference behaviour reproduced (not its implementation): operand orientation and epilogue of
+// csrc/tc_gemm.cuh:146-168,411-425; workspace split-K with last-arriver in-order reduction and counter reset
+// (:462-500); cluster split-K over distributed shared memory, bit-identical to the workspace path (:427-460);
+// weight-first streaming before the PDL dependency wait and the pdl_early rule (:386-409, 533); zero contribution
+// of K tails and out-of-range rows (here by TMA zero fill instead of predicated cp.async, :213-255).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "llg_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace llg {
+
+constexpr int kBP = 128;
+constexpr int kAtomBytes = 128;           // bytes of K per row in one swizzle atom
+constexpr int kAAtomTile = kBP * 128;     // one A atom tile in shared memory
+constexpr int kHeaderBytes = 1024;
+constexpr int kSfLag = 3;                 // block-scale cp.async groups kept in flight per thread
+
+template <int FAM, int BQ, int ATOMS>
+struct Geo {
+  static constexpr bool kMixed = FAM == FAM_W8A16 || FAM == FAM_W4A16;
+  static constexpr bool kNvf4 = FAM == FAM_NVF4;
+  static constexpr bool kIntAcc = FAM == FAM_I8;
+  static constexpr int kBPerA = FAM == FAM_W8A16 ? 2 : FAM == FAM_W4A16 ? 4 : 1;  // B atoms per A atom
+  static constexpr int kBAtomTile = BQ * 128;
+  static constexpr int kABytes = ATOMS * kAAtomTile;
+  static constexpr int kBBytes = ATOMS * kBPerA * kBAtomTile;
+  static constexpr int kSfA = (kNvf4 || FAM == FAM_W4A16) ? ATOMS * 2048 : 0;  // 128 rows x 16 scale bytes per atom
+  static constexpr int kSfB = kNvf4 ? ATOMS * 2048 : 0;
+  static constexpr int kAOff = 0, kBOff = kABytes, kSfAOff = kBOff + kBBytes, kSfBOff = kSfAOff + kSfA;
+  static constexpr int kStageBytes = (kSfBOff + kSfB + 1023) / 1024 * 1024;
+  static constexpr uint32_t kTxBytes = kABytes + kBBytes;
+  // tensor-memory columns
+  static constexpr int kAccCols = BQ < 32 ? 32 : BQ;
+  static constexpr int kAColsAtom = FAM == FAM_W8A16 ? 64 : FAM == FAM_W4A16 ? 128 : 0;  // widened A, 2 K per column
+  static constexpr int kABufs = 2;
+  static constexpr int kSfColsStage = kNvf4 ? ATOMS * 4 * 8 : 0;  // per MMA 4 columns for A scales + 4 for B
+  static constexpr int kNeedCols = kAccCols + (kMixed ? kABufs * ATOMS * kAColsAtom : 0) + 2 * kSfColsStage;
+  static constexpr int kTmemCols = kNeedCols <= 32 ? 32 : kNeedCols <= 64 ? 64 : kNeedCols <= 128 ? 128
+                                   : kNeedCols <= 256 ? 256 : 512;
+  static constexpr bool kValid = kNeedCols <= 512 && (!kNvf4 || BQ <= 128) && kStageBytes * 2 <= kSmemBudget;
+};
+
+struct SmemHeader {
+  uint64_t full[LLG_MAX_STAGES];     // TMA bytes of a stage have landed
+  uint64_t empty[LLG_MAX_STAGES];    // the MMAs that read a stage have completed
+  uint64_t sf_full[LLG_MAX_STAGES];  // block scales of a stage are in shared memory (128 arrivals)
+  uint64_t acc_full;                 // every MMA of this CTA has completed
+  uint64_t a_full[2];                // widened A buffer written to tensor memory (128 arrivals)
+  uint64_t a_empty[2];               // MMAs reading a widened A buffer have completed
+  uint32_t tmem_base;
+  uint32_t abort;
+  uint32_t last;
+};
+static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header too large");
+
+__device__ __forceinline__ void give_up(const TcDev& prm, uint32_t code) { atomicCAS(prm.status, 0u, code); }
+
+__device__ __forceinline__ float tc_vec(const float* p, int len, int i) {
+  return len == 0 ? 1.f : (len == 1 ? __ldg(p) : __ldg(p + i));
+}
+__device__ __forceinline__ float tc_bias(const TcDev& prm, int i) {
+  switch (prm.bias_dtype) {
+    case LLG_DT_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(prm.bias)[i]);
+    case LLG_DT_F16: return __half2float(static_cast<const __half*>(prm.bias)[i]);
+    default: return static_cast<const float*>(prm.bias)[i];
+  }
+}
+
+// v = ((acc * alpha) * row_scale[p]) * col_scale[q] (+ bias), every operation individually rounded.
+template <bool INT_ACC>
+__device__ __forceinline__ float tc_finish(const TcDev& prm, float alpha, int p, int q, uint32_t bits) {
+  const float acc = INT_ACC ? (float)(int32_t)bits : __uint_as_float(bits);
+  float v = __fmul_rn(__fmul_rn(__fmul_rn(acc, alpha), tc_vec(prm.row_scale, prm.row_scale_len, p)),
+                      tc_vec(prm.col_scale, prm.col_scale_len, q));
+  if (prm.bias_dtype != LLG_DT_NONE) v = __fadd_rn(v, tc_bias(prm, prm.bias_on_p ? p : q));
+  return v;
+}
+__device__ __forceinline__ void tc_store(const TcDev& prm, int p, int q, float v) {
+  const int64_t at = prm.swap ? (int64_t)q * prm.ldy + p : (int64_t)p * prm.ldy + q;
+  switch (prm.out_dtype) {
+    case LLG_DT_BF16: static_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(v); break;
+    case LLG_DT_F16: static_cast<__half*>(prm.y)[at] = __float2half_rn(v); break;
+    default: static_cast<float*>(prm.y)[at] = v; break;
+  }
+}
+
+// ---- exact widening of 8-bit / 4-bit floats to 16-bit pairs ---------------------------------------------------------
+
+// four e4m3 bytes -> (k0,k1) and (k2,k3) as bf16x2 / f16x2
+__device__ __forceinline__ void widen_e4m3x4(uint32_t w, bool bf16, uint32_t& lo, uint32_t& hi) {
+  if (bf16) {
+    // byte b -> lane (b << 8); sign stays at bit 15, exponent+mantissa move to bits 4..10, which reads as a bf16
+    // 2^-120 too small; the multiply by 2^120 is exact (also for e4m3 subnormals, which become bf16 subnormals)
+    const uint32_t a = __byte_perm(w, 0u, 0x1404), b = __byte_perm(w, 0u, 0x3424);
+    const uint32_t ta = (a & 0x80008000u) | ((a >> 4) & 0x07f007f0u), tb = (b & 0x80008000u) | ((b >> 4) & 0x07f007f0u);
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(ta), "r"(0x7b807b80u));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(tb), "r"(0x7b807b80u));
+  } else {
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"((uint16_t)(w & 0xffffu)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"((uint16_t)(w >> 16)));
+  }
+}
+// one e4m3 scale byte -> (s, s) as bf16x2 / f16x2
+__device__ __forceinline__ uint32_t widen_scale(uint32_t s, bool bf16) {
+  uint32_t lo, hi;
+  widen_e4m3x4(s | (s << 8), bf16, lo, hi);
+  return lo;
+}
+// one byte = two e2m1 nibbles (low nibble = even k) -> (k, k+1) as bf16x2 / f16x2, times the block scale pair
+__device__ __forceinline__ uint32_t widen_e2m1x2(uint32_t byte, bool bf16, uint32_t scale2) {
+  uint32_t r;
+  if (bf16) {
+    // nibble s e e m -> bf16 with the three magnitude bits at 6..8: the value times 2^-126 (e = 0 lands in the bf16
+    // subnormals, matching e2m1's 0 / 0.5); the multiply by 2^126 is exact
+    const uint32_t x = (byte & 0x0fu) | ((byte & 0xf0u) << 12);
+    const uint32_t t = ((x & 0x00080008u) << 12) | ((x & 0x00070007u) << 6);
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(t), "r"(0x7e807e80u));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(r), "r"(scale2));  // <= 6 significant bits: exact
+  } else {
+    asm("{\n\t.reg .b8 b;\n\t.reg .b16 h;\n\tcvt.u16.u32 h, %1;\n\tmov.b16 {b, _}, h;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b;\n\t}\n"
+        : "=r"(r)
+        : "r"(byte));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(r), "r"(scale2));
+  }
+  return r;
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+
+template <int FAM, int BQ, int ATOMS>
+__global__ void __launch_bounds__(kTcThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcDev prm) {
+  using G = Geo<FAM, BQ, ATOMS>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_base = smem_u32(smem_raw);
+  const uint32_t base = (raw_base + 1023u) & ~1023u;
+  SmemHeader* const hdr = reinterpret_cast<SmemHeader*>(smem_raw + (base - raw_base));
+  const uint32_t stage0 = base + kHeaderBytes;
+  volatile uint32_t* const abort_word = &hdr->abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int p0 = blockIdx.x * kBP, q0 = blockIdx.y * BQ;
+  const int split = blockIdx.z, ksplit = prm.ksplit;
+  const int S = prm.stages;
+  const int nk = (prm.k_atoms + ATOMS - 1) / ATOMS;
+  const int kt_beg = (int)((int64_t)nk * split / ksplit), kt_end = (int)((int64_t)nk * (split + 1) / ksplit);
+  const int ntiles = kt_end - kt_beg;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&hdr->full[s]), 1);
+      mbar_init(smem_u32(&hdr->empty[s]), 1);
+      mbar_init(smem_u32(&hdr->sf_full[s]), 128);
+    }
+    mbar_init(smem_u32(&hdr->acc_full), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&hdr->a_full[b]), 128);
+      mbar_init(smem_u32(&hdr->a_empty[b]), 1);
+    }
+    hdr->abort = 0u;
+    hdr->last = 0u;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&hdr->tmem_base), G::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = hdr->tmem_base;
+  if (prm.pdl_early) pdl_trigger();
+
+  constexpr uint32_t kAccCol = 0;
+  constexpr uint32_t kABufCol = G::kAccCols;                                             // mixed kinds
+  constexpr uint32_t kSfCol = G::kAccCols;                                               // nvfp4
+  const bool a_first = prm.a_is_weight != 0;  // which operand may stream before the dependency wait
+
+  if (warp == 0) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+      auto load_a = [&](int it) {
+        const int s = it % S;
+        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_2d(st + G::kAOff + a * kAAtomTile, &tmA, bar, ((kt_beg + it) * ATOMS + a) * kAtomBytes, p0,
+                      a_first ? pol_w : pol_x);
+      };
+      auto load_b = [&](int it) {
+        const int s = it % S;
+        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
+#pragma unroll
+        for (int a = 0; a < ATOMS * G::kBPerA; ++a)
+          tma_load_2d(st + G::kBOff + a * G::kBAtomTile, &tmB, bar,
+                      ((kt_beg + it) * ATOMS * G::kBPerA + a) * kAtomBytes, q0, a_first ? pol_x : pol_w);
+      };
+      const int npre = ntiles < S ? ntiles : S;
+      for (int it = 0; it < npre; ++it) {
+        mbar_expect_tx(smem_u32(&hdr->full[it]), G::kTxBytes);
+        if (a_first) load_a(it); else load_b(it);
+      }
+      pdl_wait();
+      for (int it = 0; it < npre; ++it) {
+        if (a_first) load_b(it); else load_a(it);
+      }
+      bool ok = true;
+      for (int it = npre; it < ntiles && ok; ++it) {
+        const int s = it % S;
+        ok = mbar_wait(smem_u32(&hdr->empty[s]), ((it / S) & 1) ^ 1, abort_word);
+        if (!ok) { give_up(prm, ST_PRODUCER_EMPTY_WAIT); break; }
+        mbar_expect_tx(smem_u32(&hdr->full[s]), G::kTxBytes);
+        load_a(it);
+        load_b(it);
+      }
+      if (!ok) {
+        // leave only after the copies already issued have landed (bounded): shared memory must not be written
+        // after the CTA has gone
+        for (int s = 0; s < S; ++s) {
+          const long long t0 = clock64();
+          while (!mbar_try(smem_u32(&hdr->full[s]), 0) && !mbar_try(smem_u32(&hdr->full[s]), 1) &&
+                 clock64() - t0 < kWaitCycles / 16) {}
+        }
+      }
+    }
+    __syncwarp();
+    if (!prm.pdl_early) pdl_trigger();
+    l2_prefetch_share(prm.pf, prm.pf_bytes, blockIdx.x + (int64_t)gridDim.x * (blockIdx.y + (int64_t)gridDim.y * blockIdx.z),
+                      (int64_t)gridDim.x * gridDim.y * gridDim.z, lane, 32);
+  } else if (warp == 1) {
+    // ================================ MMA issuer ================================
+    if (lane == 0) {
+      const uint32_t idesc = prm.idesc;
+      bool ok = true;
+      for (int it = 0; it < ntiles && ok; ++it) {
+        const int s = it % S;
+        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
+        ok = mbar_wait(smem_u32(&hdr->full[s]), (it / S) & 1, abort_word);
+        if constexpr (G::kNvf4) ok = ok && mbar_wait(smem_u32(&hdr->sf_full[s]), (it / S) & 1, abort_word);
+        if constexpr (G::kMixed) ok = ok && mbar_wait(smem_u32(&hdr->a_full[it & 1]), (it >> 1) & 1, abort_word);
+        if (!ok) { give_up(prm, ST_MMA_FULL_WAIT); break; }
+        tc_fence_after();
+        if constexpr (G::kMixed) {
+          const uint32_t abuf = tmem + kABufCol + (uint32_t)(it & 1) * ATOMS * G::kAColsAtom;
+          constexpr int kMmaPerAtom = G::kAColsAtom / 8;  // K = 16 per MMA, 8 columns of widened A
+#pragma unroll
+          for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+            for (int j = 0; j < kMmaPerAtom; ++j) {
+              const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + (a * G::kBPerA + j / 4) * G::kBAtomTile) + (uint64_t)((j % 4) * 2);
+              mma_ts_f16(tmem + kAccCol, abuf + a * G::kAColsAtom + j * 8, bdesc, idesc, (it | a | j) != 0);
+            }
+          umma_commit(smem_u32(&hdr->a_empty[it & 1]));
+        } else {
+          const uint32_t sfc = tmem + kSfCol + (uint32_t)(it & 1) * G::kSfColsStage;
+#pragma unroll
+          for (int a = 0; a < ATOMS; ++a) {
+            const uint64_t adesc = umma_desc_sw128(st + G::kAOff + a * kAAtomTile);
+            const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + a * G::kBAtomTile);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // 32 bytes of K per MMA for every kind
+              const uint32_t acc_on = (it | a | j) != 0;
+              if constexpr (FAM == FAM_F16) mma_ss_f16(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
+              else if constexpr (FAM == FAM_F8) mma_ss_f8f6f4(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
+              else if constexpr (FAM == FAM_I8) mma_ss_i8(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
+              else {
+                const uint32_t sfa_t = sfc + (uint32_t)(a * 4 + j) * 8, sfb_t = sfa_t + 4;
+                tmem_cp_32x128b_x4(sfa_t, umma_desc_plain128(st + G::kSfAOff + (a * 4 + j) * 512));
+                tmem_cp_32x128b_x4(sfb_t, umma_desc_plain128(st + G::kSfBOff + (a * 4 + j) * 512));
+                mma_ss_nvf4(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on, sfa_t, sfb_t);
+              }
+            }
+          }
+        }
+        umma_commit(smem_u32(&hdr->empty[s]));
+      }
+      if (ok && ntiles > 0) umma_commit(smem_u32(&hdr->acc_full));
+    }
+    __syncwarp();
+    if (!prm.pdl_early) pdl_trigger();
+  } else {
+    // ================================ converter / scale feeder, then epilogue ================================
+    const int et = tid - 64;                 // 0..127
+    const int quarter = warp & 3;            // tensor-memory lanes this warp may touch: [32*quarter, +32)
+    const int r = quarter * 32 + lane;       // row of the tile this thread owns
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    bool ok = true;
+
+    if constexpr (G::kNvf4 || FAM == FAM_W4A16) {
+      // Block scales travel by 4-byte cp.async (their rows are only 4-byte aligned); each thread moves the 16 scale
+      // bytes per atom of "its" row and keeps kSfLag stages in flight.
+      pdl_wait();
+      auto issue = [&](int it) {
+        const int s = it % S;
+        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
+        const int sfk_total = prm.K >> 4;
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+          const int sfk0 = ((kt_beg + it) * ATOMS + a) * 16;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int sfk = sfk0 + j * 4;
+            {
+              const bool v = p0 + r < prm.P && sfk < sfk_total;
+              const unsigned char* src = v ? prm.a_sf + (int64_t)(p0 + r) * prm.lda_sf + sfk : prm.a_sf;
+              const uint32_t dst = G::kNvf4 ? st + G::kSfAOff + (a * 4 + j) * 512 + (r & 31) * 16 + (r >> 5) * 4
+                                            : st + G::kSfAOff + a * 2048 + r * 16 + j * 4;
+              cp_async4_zfill(dst, src, v);
+            }
+            if constexpr (G::kNvf4) {
+              if (r < BQ) {
+                const bool v = q0 + r < prm.Q && sfk < sfk_total;
+                const unsigned char* src = v ? prm.b_sf + (int64_t)(q0 + r) * prm.ldb_sf + sfk : prm.b_sf;
+                cp_async4_zfill(st + G::kSfBOff + (a * 4 + j) * 512 + (r & 31) * 16 + (r >> 5) * 4, src, v);
+              }
+            }
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      };
+      if constexpr (G::kNvf4) {
+        // rows of the B scale blocks that no thread fills must not hold stale bytes that decode to NaN/Inf
+        for (int s = 0; s < S; ++s)
+          for (int i = et; i < G::kSfB / 4; i += 128)
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage0 + (uint32_t)s * G::kStageBytes + G::kSfBOff + i * 4), "r"(0u));
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
+      // a slot is refilled only after the MMAs that read it have completed, and those need this thread's part of the
+      // stage: the lag must stay below the ring depth
+      const int lag = S - 1 < kSfLag ? S - 1 : kSfLag;
+      for (int it = 0; it < ntiles + lag && ok; ++it) {
+        if (it < ntiles) {
+          if (it >= S) ok = mbar_wait(smem_u32(&hdr->empty[it % S]), ((it / S) & 1) ^ 1, abort_word);
+          if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
+          issue(it);
+        } else {
+          asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        const int done = it - lag;
+        if (done < 0) continue;
+        if (lag == 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
+        else if (lag == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+        else asm volatile("cp.async.wait_group 1;" ::: "memory");
+        const int s = done % S;
+        if constexpr (G::kNvf4) {
+          fence_async_shared();
+          mbar_arrive(smem_u32(&hdr->sf_full[s]));
+        } else {
+          // ---- W4A16: widen stage `done` (weight nibbles x block scale) into tensor memory ----
+          const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
+          const bool bf16 = prm.bf16_act != 0;
+          ok = mbar_wait(smem_u32(&hdr->full[s]), (done / S) & 1, abort_word) &&
+               mbar_wait(smem_u32(&hdr->a_empty[done & 1]), ((done >> 1) & 1) ^ 1, abort_word);
+          if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
+          tc_fence_after();
+          const uint32_t abuf = tmem + lane_addr + kABufCol + (uint32_t)(done & 1) * ATOMS * G::kAColsAtom;
+#pragma unroll
+          for (int a = 0; a < ATOMS; ++a) {
+            const uint4 sc = lds128(st + G::kSfAOff + a * 2048 + r * 16);
+            const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+              // chunk c holds K [32c, 32c+32) of the atom = scale blocks 2c and 2c+1
+              const uint32_t s0 = widen_scale((scw[c >> 1] >> (16 * (c & 1))) & 0xffu, bf16);
+              const uint32_t s1 = widen_scale((scw[c >> 1] >> (16 * (c & 1) + 8)) & 0xffu, bf16);
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                uint32_t o[8];
+#pragma unroll
+                for (int b = 0; b < 8; ++b)
+                  o[b] = widen_e2m1x2((w[h * 2 + b / 4] >> (8 * (b % 4))) & 0xffu, bf16, h ? s1 : s0);
+                tmem_st8(abuf + a * G::kAColsAtom + c * 16 + h * 8, o);
+              }
+            }
+          }
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(smem_u32(&hdr->a_full[done & 1]));
+        }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if constexpr (FAM == FAM_W8A16) {
+      const bool bf16 = prm.bf16_act != 0;
+      for (int it = 0; it < ntiles && ok; ++it) {
+        const int s = it % S;
+        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
+        ok = mbar_wait(smem_u32(&hdr->full[s]), (it / S) & 1, abort_word) &&
+             mbar_wait(smem_u32(&hdr->a_empty[it & 1]), ((it >> 1) & 1) ^ 1, abort_word);
+        if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
+        tc_fence_after();
+        const uint32_t abuf = tmem + lane_addr + kABufCol + (uint32_t)(it & 1) * ATOMS * G::kAColsAtom;
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+            uint32_t o[8];
+            widen_e4m3x4(raw.x, bf16, o[0], o[1]);
+            widen_e4m3x4(raw.y, bf16, o[2], o[3]);
+            widen_e4m3x4(raw.z, bf16, o[4], o[5]);
+            widen_e4m3x4(raw.w, bf16, o[6], o[7]);
+            tmem_st8(abuf + a * G::kAColsAtom + c * 8, o);
+          }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&hdr->a_full[it & 1]));
+      }
+    }
+
+    // ---------------------------------- epilogue ----------------------------------
+    pdl_wait();
+    if (ok && ntiles > 0) {
+      ok = mbar_wait(smem_u32(&hdr->acc_full), 0, abort_word);
+      if (!ok) give_up(prm, ST_EPILOGUE_WAIT);
+      tc_fence_after();
+    }
+    const bool have_acc = ok && ntiles > 0;
+    const float alpha = prm.alpha_ptr ? prm.alpha * __ldg(prm.alpha_ptr) : prm.alpha;
+    const int p = p0 + r;
+    const int nq = min(BQ, prm.Q - q0);
+    const uint32_t parked = stage0;  // cluster split-K: [BQ][128] 4-byte partials, q-major
+
+    for (int c0 = 0; c0 < BQ; c0 += 16) {
+      if (c0 >= nq) break;
+      uint32_t v[16];
+      if (have_acc) {
+        tmem_ld16(tmem + lane_addr + kAccCol + c0, v);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] = 0u;
+      }
+      if (ksplit == 1) {
+        if (p < prm.P) {
+          bool done = false;
+          if (!prm.swap && c0 + 16 <= nq) {
+            // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
+            if (prm.out_dtype == LLG_DT_F32) {
+              float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
+              if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                for (int c = 0; c < 16; c += 4) {
+                  float4 o;
+                  o.x = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
+                  o.y = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
+                  o.z = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 2, v[c + 2]);
+                  o.w = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 3, v[c + 3]);
+                  *reinterpret_cast<float4*>(dst + c) = o;
+                }
+                done = true;
+              }
+            } else {
+              uint16_t* dst = static_cast<uint16_t*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
+              if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                uint32_t o[8];
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                  const float a = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
+                  const float b = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
+                  if (prm.out_dtype == LLG_DT_BF16) {
+                    const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+                    o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                  } else {
+                    const __half2 t = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+                    o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                  }
+                }
+                *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                done = true;
+              }
+            }
+          }
+          if (!done) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]));
+          }
+        }
+      } else if (prm.cluster) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c)
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(parked + (uint32_t)((c0 + c) * kBP + r) * 4u), "r"(v[c]) : "memory");
+      } else {
+        // partial plane in the output's own element order, so both this write and the later read are coalesced
+        uint32_t* const ws = static_cast<uint32_t*>(prm.ws) + (int64_t)split * prm.P * prm.Q;
+        if (p < prm.P) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            if (c0 + c < nq) {
+              const int q = q0 + c0 + c;
+              ws[prm.swap ? (int64_t)q * prm.P + p : (int64_t)p * prm.Q + q] = v[c];
+            }
+        }
+      }
+    }
+
+    if (ksplit > 1 && !prm.cluster) {
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const unsigned tile = blockIdx.x + gridDim.x * blockIdx.y;
+      if (et == 0) hdr->last = atomicAdd(&prm.counters[tile], 1u) == (unsigned)(ksplit - 1) ? 1u : 0u;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (hdr->last) {
+        __threadfence();
+        const int np = min(kBP, prm.P - p0);
+        const int64_t plane = (int64_t)prm.P * prm.Q;
+        const uint32_t* const ws = static_cast<const uint32_t*>(prm.ws);
+        for (int i = et; i < np * nq; i += 128) {
+          const int pl = prm.swap ? i % np : i / nq, ql = prm.swap ? i / np : i % nq;
+          const int pp = p0 + pl, qq = q0 + ql;
+          const uint32_t* src = ws + (prm.swap ? (int64_t)qq * prm.P + pp : (int64_t)pp * prm.Q + qq);
+          uint32_t total = 0u;
+          for (int k0 = 0; k0 < ksplit; k0 += 8) {  // 8 loads in flight, added in split order
+            uint32_t part[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (k0 + j < ksplit) part[j] = __ldcg(src + (int64_t)(k0 + j) * plane);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (k0 + j < ksplit) {
+                if (k0 + j == 0) total = part[j];
+                else if constexpr (G::kIntAcc) total = (uint32_t)((int32_t)total + (int32_t)part[j]);
+                else total = __float_as_uint(__uint_as_float(total) + __uint_as_float(part[j]));
+              }
+          }
+          tc_store(prm, pp, qq, tc_finish<G::kIntAcc>(prm, alpha, pp, qq, total));
+        }
+        if (et == 0) prm.counters[tile] = 0u;
+      }
+    }
+  }
+
+  if (prm.cluster && ksplit > 1) {
+    // every thread of every CTA of the cluster passes both barriers, whatever happened above
+    cluster_arrive();
+    cluster_wait();
+    if (warp >= 2) {
+      const int et = tid - 64;
+      const float alpha = prm.alpha_ptr ? prm.alpha * __ldg(prm.alpha_ptr) : prm.alpha;
+      const int np = min(kBP, prm.P - p0), nq = min(BQ, prm.Q - q0);
+      const int total = kBP * nq, share = (total + ksplit - 1) / ksplit;
+      const int lo = (int)cluster_ctarank() * share, hi = min(total, lo + share);
+      for (int i = lo + et; i < hi; i += 128) {
+        const int pl = i % kBP, ql = i / kBP;
+        if (pl >= np) continue;
+        const uint32_t addr = stage0 + (uint32_t)i * 4u;
+        uint32_t part[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (k < ksplit) part[k] = ld_cluster_u32(cluster_map_shared(addr, (uint32_t)k));
+        uint32_t sum = part[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k)
+          if (k < ksplit) {
+            if constexpr (G::kIntAcc) sum = (uint32_t)((int32_t)sum + (int32_t)part[k]);
+            else sum = __float_as_uint(__uint_as_float(sum) + __uint_as_float(part[k]));
+          }
+        tc_store(prm, p0 + pl, q0 + ql, tc_finish<G::kIntAcc>(prm, alpha, p0 + pl, q0 + ql, sum));
+      }
+    }
+    cluster_arrive();  // partials stay readable until every CTA of the cluster is done with them
+    cluster_wait();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, G::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host side
+
+template <int FAM, int BQ, int ATOMS>
+cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& prm, bool pdl, cudaStream_t stream) {
+  using G = Geo<FAM, BQ, ATOMS>;
+  if constexpr (!G::kValid) {
+    return cudaErrorInvalidConfiguration;
+  } else {
+    TcDev p = prm;
+    const int cap = kSmemBudget / G::kStageBytes < LLG_MAX_STAGES ? kSmemBudget / G::kStageBytes : LLG_MAX_STAGES;
+    p.stages = prm.stages < 2 ? 2 : (prm.stages > cap ? cap : prm.stages);
+    size_t smem = 1024 + kHeaderBytes + (size_t)p.stages * G::kStageBytes;
+    if (p.ksplit == 1) p.cluster = 0;
+    if (p.cluster) {
+      if (p.ksplit > 8) return cudaErrorInvalidConfiguration;
+      const size_t need = 1024 + kHeaderBytes + (size_t)kBP * BQ * 4;
+      if (need > 227 * 1024) return cudaErrorInvalidConfiguration;
+      if (smem < need) smem = need;
+    }
+    static unsigned attr_done = 0;  // one bit per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 32 || !(attr_done & (1u << dev))) {
+      e = cudaFuncSetAttribute(umma_gemm_kernel<FAM, BQ, ATOMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return e;
+      if (dev < 32) attr_done |= 1u << dev;
+    }
+    const dim3 grid((p.P + kBP - 1) / kBP, (p.Q + BQ - 1) / BQ, p.ksplit);
+    p.pdl_early = (int64_t)grid.x * grid.y * grid.z <= sm_count();
+    return launch_ex(umma_gemm_kernel<FAM, BQ, ATOMS>, grid, dim3(kTcThreads), smem, stream, pdl,
+                     dim3(1, 1, p.cluster ? p.ksplit : 1), ta, tb, p);
+  }
+}
+
+template <int FAM>
+cudaError_t umma_launch_family(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl,
+                               cudaStream_t s) {
+  switch (cfg) {
+    case 0: return umma_launch_one<FAM, 16, 1>(ta, tb, p, pdl, s);
+    case 1: return umma_launch_one<FAM, 32, 1>(ta, tb, p, pdl, s);
+    case 2: return umma_launch_one<FAM, 64, 1>(ta, tb, p, pdl, s);
+    case 3: return umma_launch_one<FAM, 128, 1>(ta, tb, p, pdl, s);
+    case 4: return umma_launch_one<FAM, 256, 1>(ta, tb, p, pdl, s);
+    case 5: return umma_launch_one<FAM, 16, 2>(ta, tb, p, pdl, s);
+    case 6: return umma_launch_one<FAM, 32, 2>(ta, tb, p, pdl, s);
+    case 7: return umma_launch_one<FAM, 64, 2>(ta, tb, p, pdl, s);
+    case 8: return umma_launch_one<FAM, 128, 2>(ta, tb, p, pdl, s);
+    case 9: return umma_launch_one<FAM, 256, 2>(ta, tb, p, pdl, s);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+template <int FAM>
+constexpr int umma_stage_bytes(int cfg) {
+  switch (cfg) {
+    case 0: return Geo<FAM, 16, 1>::kValid ? Geo<FAM, 16, 1>::kStageBytes : 0;
+    case 1: return Geo<FAM, 32, 1>::kValid ? Geo<FAM, 32, 1>::kStageBytes : 0;
+    case 2: return Geo<FAM, 64, 1>::kValid ? Geo<FAM, 64, 1>::kStageBytes : 0;
+    case 3: return Geo<FAM, 128, 1>::kValid ? Geo<FAM, 128, 1>::kStageBytes : 0;
+    case 4: return Geo<FAM, 256, 1>::kValid ? Geo<FAM, 256, 1>::kStageBytes : 0;
+    case 5: return Geo<FAM, 16, 2>::kValid ? Geo<FAM, 16, 2>::kStageBytes : 0;
+    case 6: return Geo<FAM, 32, 2>::kValid ? Geo<FAM, 32, 2>::kStageBytes : 0;
+    case 7: return Geo<FAM, 64, 2>::kValid ? Geo<FAM, 64, 2>::kStageBytes : 0;
+    case 8: return Geo<FAM, 128, 2>::kValid ? Geo<FAM, 128, 2>::kStageBytes : 0;
+    case 9: return Geo<FAM, 256, 2>::kValid ? Geo<FAM, 256, 2>::kStageBytes : 0;
+    default: return 0;
+  }
+}
+
+}  // namespace llg

@@ -1,0 +1,12 @@
+// tcgen05 GEMM instantiations of one kernel family (all tile configs).
+#include "umma_gemm.cuh"
+
+namespace llg {
+
+cudaError_t tc_launch_i8(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s) {
+  return umma_launch_family<FAM_I8>(ta, tb, p, cfg, pdl, s);
+}
+
+int tc_stage_bytes_i8(int cfg) { return umma_stage_bytes<FAM_I8>(cfg); }
+
+}  // namespace llg

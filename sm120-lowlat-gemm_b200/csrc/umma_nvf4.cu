@@ -1,0 +1,12 @@
+// tcgen05 GEMM instantiations of one kernel family (all tile configs).
+#include "umma_gemm.cuh"
+
+namespace llg {
+
+cudaError_t tc_launch_nvf4(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl, cudaStream_t s) {
+  return umma_launch_family<FAM_NVF4>(ta, tb, p, cfg, pdl, s);
+}
+
+int tc_stage_bytes_nvf4(int cfg) { return umma_stage_bytes<FAM_NVF4>(cfg); }
+
+}  // namespace llg
