@@ -151,6 +151,10 @@ LLG_API int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* 
  * up a bounded wait; otherwise the code of the first wait that expired. No counterpart in the reference. */
 LLG_API int llg_device_status(uint32_t* status);
 
+/* sizeof(llg_skinny_args), sizeof(llg_tc_args), sizeof(llg_quant_args) as this library was compiled: lets a foreign-
+ * function binding verify its struct layout before the first call. No counterpart in the reference. */
+LLG_API void llg_struct_sizes(int32_t out[3]);
+
 LLG_API const char* llg_last_error(void);
 LLG_API int32_t llg_abi_version(void);
 

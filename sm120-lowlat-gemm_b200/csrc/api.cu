@@ -163,6 +163,11 @@ int32_t llg_abi_version(void) { return LLG_ABI_VERSION; }
 void llg_set_pdl(int32_t on) { g_pdl.store(on != 0, std::memory_order_relaxed); }
 int32_t llg_pdl_enabled(void) { return g_pdl.load(std::memory_order_relaxed) ? 1 : 0; }
 int32_t llg_smem_budget(void) { return kSmemBudget; }
+void llg_struct_sizes(int32_t out[3]) {
+  out[0] = (int32_t)sizeof(llg_skinny_args);
+  out[1] = (int32_t)sizeof(llg_tc_args);
+  out[2] = (int32_t)sizeof(llg_quant_args);
+}
 
 int llg_device_status(uint32_t* status) {
   unsigned int* dptr = status_word_device_ptr();
