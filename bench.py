@@ -1,0 +1,400 @@
+"""Benchmark of the low-latency GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N = 1  workload "c2_fp8_decode": BASELINE config 2, W8A8 FP8 y[M,14336] = x[M,4096] @ w[14336,4096]^T with per-token
+       activation scales, per-channel weight scales, bf16 output. One step = the five decode GEMMs M = 1, 2, 4, 8, 16,
+       each on a different weight copy (copies rotate over > 512 MB, four times the L2, so every GEMM streams its weight
+       from HBM). metric = achieved HBM GB/s = algorithmic bytes of the step / device time.
+N > 1  workload "c5_tp_decode_step": BASELINE config 5, tensor-parallel decode layers (hidden 8192, QKV 10240,
+       gate_up 57344, down 28672) in FP8 at M = 8, sharded over the N GPUs with an NCCL all-reduce after each
+       row-parallel GEMM; strong scaling; the same metric (aggregate algorithmic bytes / max-over-ranks device time).
+--impl reference: the reference semantics on the host cores (dequantise, torch fp32 matmul), the only CPU
+       implementation this path has (the reference itself is CUDA-only).
+Prints one JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT / "sm120-lowlat-gemm_b200", ROOT):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import torch  # noqa: E402
+
+N_OUT, K_IN = 14336, 4096
+TOKENS = (1, 2, 4, 8, 16)
+TP_M = 8
+TP_KIND = "fp8"
+
+
+def peaks() -> dict:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.is_file():
+        d = json.loads(f.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.stop, self.index = [], threading.Event(), index
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _sample(self):
+        try:
+            out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                 capture_output=True, text=True, timeout=10).stdout.strip().splitlines()
+            if out:
+                self.rows.append([c.strip() for c in out[0].split(",")])
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self.stop.is_set():
+            self._sample()
+            self.stop.wait(0.1)
+
+    def __enter__(self):
+        self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        self.t.join(timeout=15)
+        if not self.rows:
+            self._sample()
+
+    def summary(self) -> dict:
+        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows for n, v in zip(names, r[2:]) if v.lower().startswith("active")})
+        mx = max((int(r[1]) for r in self.rows if r[1].isdigit()), default=0)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else 0, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+def step_bytes() -> int:
+    from lowlat_gemm import timing
+    return sum(timing.algorithmic_bytes("fp8", m, N_OUT, K_IN, 2, m, N_OUT) for m in TOKENS)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# CPU legs (oracle port of the reference semantics; the reference has no CPU implementation of its own)
+
+
+def cpu_step_seconds(reps: int) -> tuple[float, int]:
+    """Median seconds of one c2 step on the host: dequantise w and x to fp32, torch.matmul, scale, round to bf16."""
+    import numpy as np
+    from oracle import oracle as O
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    w8 = (torch.randn(N_OUT, K_IN, generator=g) * 4).to(torch.float8_e4m3fn)
+    ws = (torch.rand(N_OUT, generator=g) * 1.5 + 0.5) * 1e-3
+    table = torch.from_numpy(O.E4M3_VALUES.astype(np.float32))
+    xs_all = {m: torch.randn(m, K_IN, generator=g) for m in TOKENS}
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for m in TOKENS:
+            xq, s = O.quantize_fp8(xs_all[m].numpy())
+            xd = table[torch.from_numpy(xq.astype(np.int64))] * torch.from_numpy(s)[:, None]
+            wd = table[w8.view(torch.uint8).long()] * ws[:, None]           # dequantised weight, fp32
+            y = (xd @ wd.T).to(torch.bfloat16)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2], threads
+
+
+def cpu_tp_layer_seconds() -> tuple[float, int, int]:
+    """Seconds of ONE config-5 decode layer (TP1 shapes, FP8 weights, M = 8) on the host, and its weight bytes."""
+    import numpy as np
+    from oracle import oracle as O
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    table = torch.from_numpy(O.E4M3_VALUES.astype(np.float32))
+    shapes = [(10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672)]
+    x = torch.randn(TP_M, 8192, generator=g)
+    total, nbytes = 0.0, 0
+    for n, k in shapes:
+        w8 = torch.randint(0, 0x7E, (n, k), generator=g, dtype=torch.uint8)
+        ws = torch.rand(n, generator=g) * 1e-3
+        xin = torch.randn(TP_M, k, generator=g)
+        t0 = time.perf_counter()
+        xq, s = O.quantize_fp8(xin.numpy())
+        xd = table[torch.from_numpy(xq.astype(np.int64))] * torch.from_numpy(s)[:, None]
+        y = torch.empty(TP_M, n)
+        for r0 in range(0, n, 8192):  # dequantise in row blocks to bound host memory
+            wd = table[w8[r0:r0 + 8192].long()] * ws[r0:r0 + 8192, None]
+            y[:, r0:r0 + 8192] = xd @ wd.T
+        total += time.perf_counter() - t0
+        nbytes += n * k
+        del w8
+    return total, threads, nbytes
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if args.gpus > 1:
+        sec, threads, nbytes = cpu_tp_layer_seconds()
+        gbs = nbytes / sec / 1e9
+        line = {"impl": "reference", "metric": "decode_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * args.layers, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+                "config": {"workload": "c5_tp_decode_step", "hidden": 8192, "qkv": 10240, "gate_up": 57344, "down": 28672,
+                           "tokens": TP_M, "layers": args.layers, "parallelism": "host cpu"},
+                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                                 "sample": "one decode layer (4 FP8 GEMMs, M=8, TP1 shapes): dequantise + fp32 torch.matmul on the host; "
+                                           "ms_per_step extrapolates to the step's layers"},
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+    for _ in range(min(args.warmup, 1)):
+        cpu_step_seconds(1)
+    reps = max(1, min(args.steps, 5))
+    sec, threads = cpu_step_seconds(reps)
+    gbs = step_bytes() / sec / 1e9
+    line = {"impl": "reference", "metric": "decode_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+            "config": {"workload": "c2_fp8_decode", "n": N_OUT, "k": K_IN, "tokens": list(TOKENS)},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                             "sample": f"median of {reps} c2 steps (5 GEMMs each, dequantise + fp32 torch.matmul) on the host"},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# N = 1: config 2
+
+
+def replay_timed(graphs_and_counts, total_steps: int) -> float:
+    """Replays graphs so that exactly total_steps steps run; returns device milliseconds between CUDA events."""
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    left = total_steps
+    for graph, n in graphs_and_counts:
+        while left >= n and n > 0:
+            graph.replay()
+            left -= n
+    b.record()
+    torch.cuda.synchronize()
+    assert left == 0
+    return a.elapsed_time(b)
+
+
+def capture(fn_step, nsteps: int):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(nsteps):
+            fn_step(i)
+    return g
+
+
+def run_single(args) -> None:
+    import lowlat_gemm as L
+    from lowlat_gemm import timing
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    L.set_pdl(not args.no_pdl)
+    cold = timing.ColdWeights("fp8", N_OUT, K_IN, dev)
+    gen = torch.Generator().manual_seed(0)
+    x_host = {m: torch.randn(m, K_IN, generator=gen).to(torch.bfloat16).pin_memory() for m in TOKENS}
+    x_dev = {m: x_host[m].to(dev) for m in TOKENS}
+    xq = {m: L.quantize_fp8(x_dev[m]) for m in TOKENS}            # resident, pre-quantised inputs for `value`
+    y_dev = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16, device=dev) for m in TOKENS}
+    y_host = {m: torch.empty(m, N_OUT, dtype=torch.bfloat16).pin_memory() for m in TOKENS}
+    elems = cnts = 0
+    for m in TOKENS:
+        e, c = L.workspace_need("fp8", N_OUT, K_IN, m, dev)
+        elems, cnts = max(elems, e), max(cnts, c)
+    L.reserve_workspace(dev, elems, cnts)
+    ncopies = len(cold)
+    pos = [0]
+
+    def weights():
+        w, kw = cold.items[pos[0] % ncopies]
+        pos[0] += 1
+        return w, kw
+
+    def kernel_step(_i):  # inputs resident in HBM
+        for m in TOKENS:
+            w, kw = weights()
+            L.gemm(xq[m][0], w, x_scale=xq[m][1], out=y_dev[m], **kw)
+
+    def e2e_step(_i):  # the call a user makes, from pinned host activations to pinned host results
+        for m in TOKENS:
+            w, kw = weights()
+            x_dev[m].copy_(x_host[m], non_blocking=True)
+            q, s = L.quantize_fp8(x_dev[m])
+            L.gemm(q, w, x_scale=s, out=y_dev[m], **kw)
+            y_host[m].copy_(y_dev[m], non_blocking=True)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        kernel_step(0)
+        e2e_step(0)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+
+    chunk = min(args.steps, 64)
+    rem = args.steps % chunk
+    with torch.cuda.stream(side):
+        graphs = [(capture(kernel_step, chunk), chunk)] + ([(capture(kernel_step, rem), rem)] if rem else [])
+        egraphs = [(capture(e2e_step, chunk), chunk)] + ([(capture(e2e_step, rem), rem)] if rem else [])
+    torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        graphs[0][0].replay()
+        egraphs[0][0].replay()
+    torch.cuda.synchronize()
+    with ClockSampler(0) as clk:
+        ms = replay_timed(graphs, args.steps)
+        ms_e2e = replay_timed(egraphs, args.steps)
+        if ms + ms_e2e < 400:  # keep the GPU busy long enough for the sampler to see loaded clocks
+            t_end = time.time() + 0.5
+            while time.time() < t_end:
+                graphs[0][0].replay()
+            torch.cuda.synchronize()
+    sb = step_bytes()
+    value = sb * args.steps / (ms * 1e-3) / 1e9
+    e2e = sb * args.steps / (ms_e2e * 1e-3) / 1e9
+    launches = args.steps * len(TOKENS)
+    pk = peaks()
+    per_launch_bytes = sb / len(TOKENS)
+    per_launch_us = ms * 1e3 / launches
+    achieved = per_launch_bytes / (per_launch_us * 1e-6) / 1e9
+    cpu_sec, threads = cpu_step_seconds(3)
+    from lowlat_gemm import _native
+    status = _native.device_status()
+    line = {
+        "metric": "decode_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+        "config": {"workload": "c2_fp8_decode", "n": N_OUT, "k": K_IN, "tokens": list(TOKENS), "out": "bf16",
+                   "cold_weights": f"{ncopies} weight copies rotate ({ncopies * cold.nbytes >> 20} MB > 4x L2)",
+                   "pdl": L.pdl_enabled(), "launch": "cuda_graph", "us_per_gemm": per_launch_us,
+                   "pct_of_8tbs": 100 * value / 8000.0},
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": sum(m * K_IN * 2 for m in TOKENS),
+                "d2h_bytes_per_step": sum(m * N_OUT * 2 for m in TOKENS), "ms_per_step": ms_e2e / args.steps,
+                "path": "pinned host x -> H2D -> quantize_fp8 -> gemm -> D2H pinned y, captured in a CUDA graph"},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                     "kernel": "umma_gemm_kernel<FAM_F8,16,1>", "algorithmic_bytes_per_launch": per_launch_bytes},
+        "cpu_baseline": {"value": sb / cpu_sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": "median of 3 c2 steps (5 GEMMs each, dequantise + fp32 torch.matmul) on the host"},
+        "clocks": clk.summary(), "device_status": status,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# N > 1: config 5, tensor-parallel decode step
+
+
+def run_tp(args) -> None:
+    import torch.distributed as dist
+    import lowlat_gemm as L
+    from lowlat_gemm import tp as TP
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    L.set_pdl(not args.no_pdl)
+    layers = args.layers
+    step = TP.DecodeStep(TP_KIND, layers, world, rank, dev, prefetch_bytes=0)
+    x = torch.randn(TP_M, step.shape.hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).to(torch.bfloat16) * 0.05
+    elems = cnts = 0
+    for n, k in step.shape.shards(world).values():
+        e, c = L.workspace_need(TP_KIND, n, k, TP_M, dev)
+        elems, cnts = max(elems, e), max(cnts, c)
+    L.reserve_workspace(dev, elems, cnts)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step.run(x)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    step.gemms = step.collectives = 0
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step.run(x)
+    gemms_per_step = step.gemms
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clk:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+    dist.barrier()
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    total_bytes = step.weight_bytes() * world  # every rank streams its shard; activations are negligible
+    if rank == 0:
+        value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+        pk = peaks()
+        line = {"metric": "decode_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
+                "config": {"workload": "c5_tp_decode_step", "hidden": 8192, "qkv": 10240, "gate_up": 57344, "down": 28672,
+                           "tokens": TP_M, "layers": layers, "parallelism": f"tp{world}", "collective": "nccl all_reduce x2 per layer",
+                           "us_per_layer": ms * 1e3 / args.steps / layers, "pdl": L.pdl_enabled(), "launch": "cuda_graph",
+                           "cold_weights": f"{layers} layers of distinct weights ({step.weight_bytes() >> 20} MB per rank)"},
+                "e2e": None, "gpu_launches": args.steps * gemms_per_step * 2,
+                "roofline": {"bound": "hbm", "achieved": value / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": value / world / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                             "note": "per-GPU weight bytes of the step / step time, collectives included"},
+                "cpu_baseline": None, "clocks": clk.summary()}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--layers", type=int, default=8)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_tp(args)
+    else:
+        run_single(args)
+
+
+if __name__ == "__main__":
+    main()

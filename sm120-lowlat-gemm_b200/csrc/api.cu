@@ -388,6 +388,9 @@ int llg_quant(const llg_quant_args* a, void* stream) {
   if (!a) return fail(LLG_E_INVALID, "null arguments");
   if (a->in_dtype < LLG_DT_BF16 || a->in_dtype > LLG_DT_F32) return fail(LLG_E_INVALID, "quant: x must be bf16, f16 or f32");
   if (a->M < 0 || a->K < 0) return fail(LLG_E_INVALID, "quant: x must be a 2-D CUDA tensor with unit last stride");
+  if (a->mode < LLG_QUANT_FP8_STATIC || a->mode > LLG_QUANT_NVFP4) return fail(LLG_E_INVALID, "quant: unknown mode %d", a->mode);
+  if (a->mode == LLG_QUANT_NVFP4 && a->K % 16) return fail(LLG_E_INVALID, "quant: nvfp4 needs K %% 16 == 0");
+  if (a->M == 0 || a->K == 0) return LLG_OK;  // empty: nothing to launch (and empty tensors have null pointers)
   switch (a->mode) {
     case LLG_QUANT_FP8_STATIC:
       if (!a->scale_in) return fail(LLG_E_INVALID, "quant: this mode needs scale_in float32[1]");
@@ -396,15 +399,12 @@ int llg_quant(const llg_quant_args* a, void* stream) {
     case LLG_QUANT_INT8_PER_TOKEN:
       if (!a->scale_out) return fail(LLG_E_INVALID, "quant: per-token modes need scale_out float32[M]");
       break;
-    case LLG_QUANT_NVFP4:
-      if (a->K % 16) return fail(LLG_E_INVALID, "quant: nvfp4 needs K %% 16 == 0");
+    default:
       if (a->ldq % 8 || !aligned(a->q, 8)) return fail(LLG_E_INVALID, "quant: q must be [M, K/2] bytes with 8-byte aligned rows");
       if (!a->sf_out) return fail(LLG_E_INVALID, "quant: nvfp4 needs sf [M, K/16] bytes");
       if (!a->scale_in) return fail(LLG_E_INVALID, "quant: this mode needs scale_in float32[1]");
       break;
-    default: return fail(LLG_E_INVALID, "quant: unknown mode %d", a->mode);
   }
-  if (a->M == 0 || a->K == 0) return LLG_OK;
   if (!a->x || !a->q) return fail(LLG_E_INVALID, "quant: q must be a 2-D 1-byte tensor with M rows");
   const cudaError_t e = quant_launch(*a, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {

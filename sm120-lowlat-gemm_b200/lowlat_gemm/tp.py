@@ -1,0 +1,142 @@
+"""Tensor-parallel decode step over the GEMM library: one process per GPU, weights sharded Megatron-style.
+
+Per layer (hidden H, intermediate I; the attention itself is outside the GEMM path and is stood in for by a slice):
+    qkv      [QKV/tp, H]   column-parallel (no communication)
+    o        [H, H/tp]     row-parallel    -> all-reduce(sum) of y[M, H]
+    gate_up  [2*I/tp, H]   column-parallel, gate and up halves sharded separately so SiLU(gate)*up stays local
+    down     [H, I/tp]     row-parallel    -> all-reduce(sum) of y[M, H]
+The reference has no multi-GPU code; its nearest analogue is the single-GPU step replay tools/decode_step.py:27-172,
+whose structure (per-layer weights so every GEMM streams from HBM, one CUDA graph per variant, PDL and next-weight
+prefetch as options) this module keeps.
+
+The GEMM and quantizer callables are parameters so the sharding and collective logic can run on CPU ranks (gloo) in
+tests with a host matmul; the defaults are the library's own CUDA entry points.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import timing
+
+FP8 = torch.float8_e4m3fn
+
+
+@dataclass(frozen=True)
+class LayerShape:
+    hidden: int = 8192
+    qkv: int = 10240
+    inter: int = 28672
+
+    def shards(self, tp: int) -> dict[str, tuple[int, int]]:
+        """Per-rank (N, K) of the four projections."""
+        for v in (self.qkv, self.hidden, self.inter):
+            if v % tp:
+                raise ValueError(f"{v} is not divisible by tp={tp}")
+        return {"qkv": (self.qkv // tp, self.hidden), "o": (self.hidden, self.hidden // tp),
+                "gate_up": (2 * self.inter // tp, self.hidden), "down": (self.hidden, self.inter // tp)}
+
+
+def shard_rows(w: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+    """Column-parallel shard: a contiguous block of output rows."""
+    n = w.shape[0] // tp
+    return w[rank * n:(rank + 1) * n]
+
+
+def shard_cols(w: torch.Tensor, tp: int, rank: int, per_elem: int = 1) -> torch.Tensor:
+    """Row-parallel shard: a contiguous block of K columns (per_elem = stored columns per K element, e.g. 1/2 for fp4
+    is expressed by the caller passing the packed width)."""
+    k = w.shape[1] // tp
+    return w[:, rank * k:(rank + 1) * k].contiguous()
+
+
+def shard_gate_up(w: torch.Tensor, tp: int, rank: int) -> torch.Tensor:
+    """gate_up [2I, H] = [gate; up]: each half is sharded by rows and the two shards are stacked again."""
+    half = w.shape[0] // 2
+    n = half // tp
+    return torch.cat([w[rank * n:(rank + 1) * n], w[half + rank * n: half + (rank + 1) * n]], dim=0)
+
+
+class DecodeLayer:
+    """One rank's shard of one layer, with synthetic weights of the requested precision."""
+
+    def __init__(self, kind: str, shape: LayerShape, tp: int, rank: int, device, seed: int = 0):
+        self.kind, self.shape, self.tp, self.rank = kind, shape, tp, rank
+        g = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
+        self.w = {name: timing.make_weight(kind, n, k, g, device) for name, (n, k) in shape.shards(tp).items()}
+
+    def weight_bytes(self) -> int:
+        return sum(timing.weight_bytes(self.kind, *nk) for nk in self.shape.shards(self.tp).values())
+
+
+def _default_fns():
+    from . import api
+    return api.gemm, api.quantize_fp8, api.quantize_nvfp4
+
+
+class DecodeStep:
+    """`layers` decode layers on this rank; run() executes them in order on the current stream."""
+
+    def __init__(self, kind: str, layers: int, tp: int, rank: int, device, shape: LayerShape = LayerShape(), group=None,
+                 gemm_fn=None, prefetch_bytes: int = 0, nvfp4_global: float = 64.0):
+        self.kind, self.tp, self.rank, self.group, self.device = kind, tp, rank, group, device
+        self.shape = shape
+        self.layers = [DecodeLayer(kind, shape, tp, rank, device, seed=i) for i in range(layers)]
+        g, q8, q4 = _default_fns() if gemm_fn is None else (gemm_fn, None, None)
+        self._gemm, self._q8, self._q4 = g, q8, q4
+        self.prefetch_bytes = prefetch_bytes
+        self.act_dtype = torch.float16 if kind.endswith("f16") and not kind.endswith("bf16") else torch.bfloat16
+        self._g4 = torch.tensor([nvfp4_global], device=device) if kind == "nvfp4" else None
+        self._g4_host = float(nvfp4_global)  # host copy: nothing on the launch path may read the device
+        self.collectives = 0
+        self.gemms = 0
+
+    def weight_bytes(self) -> int:
+        return sum(l.weight_bytes() for l in self.layers)
+
+    def _order(self):
+        return [(li, name) for li in range(len(self.layers)) for name in ("qkv", "o", "gate_up", "down")]
+
+    def _project(self, h: torch.Tensor, w, kw: dict, nxt) -> torch.Tensor:
+        """One projection: activation quantization where the precision needs it, then the GEMM."""
+        extra = {}
+        if nxt is not None and self.prefetch_bytes:
+            extra = {"prefetch": nxt, "prefetch_bytes": min(self.prefetch_bytes, nxt.numel() * nxt.element_size())}
+        self.gemms += 1
+        if self.kind == "fp8":
+            q, s = self._q8(h)
+            return self._gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
+        if self.kind == "nvfp4":
+            q, sf = self._q4(h, self._g4)
+            return self._gemm(q, w, x_block_scale=sf, x_scale=1.0 / self._g4_host, out_dtype=self.act_dtype, **kw, **extra)
+        return self._gemm(h, w, out_dtype=self.act_dtype, **kw, **extra)
+
+    def _all_reduce(self, y: torch.Tensor) -> None:
+        if self.tp > 1:
+            dist.all_reduce(y, group=self.group)
+            self.collectives += 1
+
+    def run(self, x: torch.Tensor) -> torch.Tensor:
+        """x [M, hidden] replicated on every rank -> [M, hidden] replicated (after the last all-reduce)."""
+        order = self._order()
+        nxt_w = {order[i]: self.layers[order[(i + 1) % len(order)][0]].w[order[(i + 1) % len(order)][1]][0]
+                 for i in range(len(order))}
+        sh = self.shape
+        a_width = sh.hidden // self.tp
+        for li, layer in enumerate(self.layers):
+            qkv = self._project(x, *layer.w["qkv"], nxt_w[(li, "qkv")])
+            attn = qkv[:, :a_width]  # stand-in for this rank's attention heads' output
+            if attn.data_ptr() % 16 or (attn.stride(0) * attn.element_size()) % 16:
+                attn = attn.contiguous()  # the GEMM takes strided rows as long as they stay 16-byte aligned
+            o = self._project(attn, *layer.w["o"], nxt_w[(li, "o")])
+            self._all_reduce(o)
+            gu = self._project(o, *layer.w["gate_up"], nxt_w[(li, "gate_up")])
+            half = gu.shape[1] // 2
+            act = torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]
+            d = self._project(act, *layer.w["down"], nxt_w[(li, "down")])
+            self._all_reduce(d)
+            x = d
+        return x
