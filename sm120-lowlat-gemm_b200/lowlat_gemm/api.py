@@ -54,6 +54,7 @@ def reserve_workspace(device: torch.device, elems: int, counters: int) -> None:
 
 
 def _workspace(device: torch.device, elems: int, counters: int):
+    device = _dev(device)
     reserve_workspace(device, elems, counters)
     return _ws[device.index]
 
