@@ -151,6 +151,26 @@ LLG_API int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* 
  * up a bounded wait; otherwise the code of the first wait that expired. No counterpart in the reference. */
 LLG_API int llg_device_status(uint32_t* status);
 
+/* Split-K tensor-core GEMM for callers that must not allocate device memory. Same arguments and result as
+ * llg_tc_gemm, except that args->ws / args->counters are ignored: partial sums and arrival counters live in a fixed
+ * scratch array inside the library (LLG_STATIC_WS_ELEMS 4-byte partials + LLG_STATIC_COUNTERS counters, about 4 MB,
+ * held by every GPU that loads the library until the process exits). Meant for hosts that own all device memory
+ * themselves - an inference server that carved the GPU into its own pools at start-up, a plugin sandbox or a
+ * real-time loop where cudaMalloc is forbidden because it synchronises the device and may fail late - and so cannot
+ * hand this library a workspace tensor. The call itself performs no cudaMalloc / cudaFree and calls no allocating
+ * library routine.
+ *   - A problem needing more than the fixed scratch (ksplit * P * Q partials, one counter per output tile) is
+ *     rejected with LLG_E_INVALID and a message that names both numbers.
+ *   - The first call on each device looks up the scratch address (one cudaGetSymbolAddress with that device current);
+ *     make that first call outside any stream capture.
+ *   - Every call on a device shares the one array: the counters the launch needs are cleared on the stream before the
+ *     kernel, the partials are fully rewritten before they are read, and two calls that overlap on the GPU (different
+ *     streams) race with each other - keep calls that use it on one stream.
+ * This entry point has no counterpart in the reference, whose callers always pass workspace tensors. */
+#define LLG_STATIC_WS_ELEMS (1 << 20)
+#define LLG_STATIC_COUNTERS 4096
+LLG_API int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream);
+
 /* sizeof(llg_skinny_args), sizeof(llg_tc_args), sizeof(llg_quant_args) as this library was compiled: lets a foreign-
  * function binding verify its struct layout before the first call. No counterpart in the reference. */
 LLG_API void llg_struct_sizes(int32_t out[3]);

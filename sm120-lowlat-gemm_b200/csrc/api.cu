@@ -44,6 +44,11 @@ std::atomic<bool> g_pdl{false};
 
 __device__ unsigned int g_status_word = 0;
 
+// Fixed split-K scratch of llg_tc_gemm_static_ws: partials first, arrival counters behind them. In host code this
+// name is only a handle for cudaGetSymbolAddress, never a device address.
+constexpr size_t kStaticWsBytes = (size_t)LLG_STATIC_WS_ELEMS * 4, kStaticCntBytes = (size_t)LLG_STATIC_COUNTERS * 4;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticWsBytes + kStaticCntBytes];
+
 struct KindSpec {
   int a_bits, b_bits;
   bool a_sf, b_sf;
@@ -368,6 +373,49 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
                 "config %d cannot be launched for this kind: %s", a->cfg, cudaGetErrorString(e));
   }
   return LLG_OK;
+}
+
+int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream) {
+  if (!args) return fail(LLG_E_INVALID, "null arguments");
+  // set-up, once per device, with that device current: the device address of the scratch array
+  static unsigned char* base[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail("cudaGetDevice", e);
+  if (dev < 0 || dev >= 64) return fail(LLG_E_INVALID, "device index %d not supported by the static workspace", dev);
+  unsigned char* ptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!base[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess) return cuda_fail("cudaGetSymbolAddress(static workspace)", e);
+      base[dev] = static_cast<unsigned char*>(p);
+    }
+    ptr = base[dev];
+  }
+  llg_tc_args a = *args;
+  a.ws = nullptr; a.ws_elems = 0; a.counters = nullptr; a.counters_elems = 0;
+  const bool cluster = a.cluster && a.ksplit > 1;
+  if (a.ksplit > 1 && !cluster) {
+    const TcTile tile = tc_tile_of(a.cfg);
+    if (tile.bq == 0) return fail(LLG_E_INVALID, "cfg must be in [0, %d), got %d", LLG_NUM_CFGS, a.cfg);
+    const int64_t need = (int64_t)a.ksplit * a.a_rows * a.b_rows;
+    const int64_t tiles = ((a.a_rows + 127) / 128) * ((a.b_rows + tile.bq - 1) / tile.bq);
+    if (a.a_rows < 1 || a.b_rows < 1 || need > LLG_STATIC_WS_ELEMS || tiles > LLG_STATIC_COUNTERS)
+      return fail(LLG_E_INVALID, "static workspace too small: this GEMM needs %lld partials and %lld counters, the built-in "
+                  "scratch holds %d and %d; use llg_tc_gemm with a caller-provided workspace", (long long)need,
+                  (long long)tiles, LLG_STATIC_WS_ELEMS, LLG_STATIC_COUNTERS);
+    a.ws = ptr;
+    a.ws_elems = LLG_STATIC_WS_ELEMS;
+    a.counters = reinterpret_cast<int32_t*>(ptr + kStaticWsBytes);
+    a.counters_elems = LLG_STATIC_COUNTERS;
+    // the array keeps whatever the last call left: the counters of this launch must start at zero
+    e = cudaMemsetAsync(a.counters, 0, (size_t)tiles * 4, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail("clearing the static counters", e);
+  }
+  return llg_tc_gemm(&a, stream);
 }
 
 int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* x_dev, int64_t x_bytes, void* y_host,
