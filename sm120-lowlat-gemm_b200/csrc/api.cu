@@ -145,6 +145,11 @@ int tc_family_of(int kind) {
   }
 }
 
+int tc_threads_of(int kind) {
+  const int f = tc_family_of(kind);
+  return (f == FAM_NVF4 || f == FAM_W8A16 || f == FAM_W4A16) ? 320 : 192;
+}
+
 int tc_stage_bytes_of(int kind, int cfg) {
   switch (tc_family_of(kind)) {
     case FAM_F16: return tc_stage_bytes_f16(cfg);
@@ -195,7 +200,7 @@ int llg_tc_info(int32_t kind, int32_t cfg, int32_t out[4]) {
   if (t.bq == 0 || tc_family_of(kind) < 0) return fail(LLG_E_INVALID, "unknown kind %d or cfg %d", kind, cfg);
   out[0] = 128;
   out[1] = t.bq;
-  out[2] = kTcThreads;
+  out[2] = tc_threads_of(kind);
   out[3] = tc_stage_bytes_of(kind, cfg);
   return LLG_OK;
 }

@@ -97,6 +97,7 @@ struct TcDev {
   int P, Q, K;          // K in elements
   int k_atoms;          // ceil(K bytes of the streamed (narrower) operand per row / 128)
   int ksplit, stages;
+  int n_items;          // (tile, K partition) pairs a persistent grid walks; 1 per CTA in cluster mode
   uint32_t idesc;
   // split-K
   void* ws;
@@ -116,7 +117,7 @@ TcTile tc_tile_of(int cfg);
 int tc_family_of(int kind);
 // bytes per stage of (family, cfg); 0 if invalid
 int tc_stage_bytes_of(int kind, int cfg);
-constexpr int kTcThreads = 192;
+int tc_threads_of(int kind);  // 192, or 320 for the kinds with helper warps (block scales / widening)
 constexpr int kSmemBudget = 227 * 1024 - 2048;  // dynamic shared memory for stages; the rest holds barriers and slack
 
 // Defined per family in umma_<family>.cu.

@@ -35,6 +35,8 @@ struct Geo {
   static constexpr bool kMixed = FAM == FAM_W8A16 || FAM == FAM_W4A16;
   static constexpr bool kNvf4 = FAM == FAM_NVF4;
   static constexpr bool kIntAcc = FAM == FAM_I8;
+  static constexpr bool kHelpers = kMixed || kNvf4;              // warps 6-9: converter / block-scale feeder
+  static constexpr int kThreads = kHelpers ? 320 : 192;
   static constexpr int kBPerA = FAM == FAM_W8A16 ? 2 : FAM == FAM_W4A16 ? 4 : 1;  // B atoms per A atom
   static constexpr int kBAtomTile = BQ * 128;
   static constexpr int kABytes = ATOMS * kAAtomTile;
@@ -44,12 +46,14 @@ struct Geo {
   static constexpr int kAOff = 0, kBOff = kABytes, kSfAOff = kBOff + kBBytes, kSfBOff = kSfAOff + kSfA;
   static constexpr int kStageBytes = (kSfBOff + kSfB + 1023) / 1024 * 1024;
   static constexpr uint32_t kTxBytes = kABytes + kBBytes;
-  // tensor-memory columns
+  // tensor-memory columns: accumulator buffers first, then widened-A buffers or block-scale columns
   static constexpr int kAccCols = BQ < 32 ? 32 : BQ;
   static constexpr int kAColsAtom = FAM == FAM_W8A16 ? 64 : FAM == FAM_W4A16 ? 128 : 0;  // widened A, 2 K per column
   static constexpr int kABufs = 2;
   static constexpr int kSfColsStage = kNvf4 ? ATOMS * 4 * 8 : 0;  // per MMA 4 columns for A scales + 4 for B
-  static constexpr int kNeedCols = kAccCols + (kMixed ? kABufs * ATOMS * kAColsAtom : 0) + 2 * kSfColsStage;
+  static constexpr int kOtherCols = (kMixed ? kABufs * ATOMS * kAColsAtom : 0) + 2 * kSfColsStage;
+  static constexpr int kAccBufs = 2 * kAccCols + kOtherCols <= 512 ? 2 : 1;  // two: epilogue overlaps the next item
+  static constexpr int kNeedCols = kAccBufs * kAccCols + kOtherCols;
   static constexpr int kTmemCols = kNeedCols <= 32 ? 32 : kNeedCols <= 64 ? 64 : kNeedCols <= 128 ? 128
                                    : kNeedCols <= 256 ? 256 : 512;
   static constexpr bool kValid = kNeedCols <= 512 && (!kNvf4 || BQ <= 128) && kStageBytes * 2 <= kSmemBudget;
@@ -59,7 +63,8 @@ struct SmemHeader {
   uint64_t full[LLG_MAX_STAGES];     // TMA bytes of a stage have landed
   uint64_t empty[LLG_MAX_STAGES];    // the MMAs that read a stage have completed
   uint64_t sf_full[LLG_MAX_STAGES];  // block scales of a stage are in shared memory (128 arrivals)
-  uint64_t acc_full;                 // every MMA of this CTA has completed
+  uint64_t acc_full[2];              // every MMA of the item that used this accumulator buffer has completed
+  uint64_t acc_empty[2];             // the epilogue has read the buffer out (128 arrivals)
   uint64_t a_full[2];                // widened A buffer written to tensor memory (128 arrivals)
   uint64_t a_empty[2];               // MMAs reading a widened A buffer have completed
   uint32_t tmem_base;
@@ -148,9 +153,41 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Work decomposition. An item is one (output tile, K partition). Without cluster split-K the kernel is persistent: the
+// grid holds at most as many CTAs as fit on the GPU at once and CTA c works on items c, c + grid, c + 2*grid, ...;
+// the TMA ring, the stage counters and (where tensor memory allows) two accumulator buffers carry across items, so
+// the loads of the next item and the epilogue of the previous one overlap the MMAs of the current one. With cluster
+// split-K every CTA owns exactly one item (tile = blockIdx.x, partition = rank in the cluster).
+
+struct Item {
+  int p0, q0, split, kt_beg, ntiles;
+  unsigned tile;
+};
+
+template <int BQ, int ATOMS>
+__device__ __forceinline__ Item decode_item(const TcDev& prm, int item) {
+  const int tiles_p = (prm.P + kBP - 1) / kBP, tiles_q = (prm.Q + BQ - 1) / BQ;
+  const int ntile = tiles_p * tiles_q;
+  Item w;
+  int tile;
+  if (prm.cluster) {
+    tile = blockIdx.x;
+    w.split = blockIdx.z;
+  } else {
+    tile = item % ntile;
+    w.split = item / ntile;
+  }
+  w.tile = (unsigned)tile;
+  w.p0 = (tile % tiles_p) * kBP;
+  w.q0 = (tile / tiles_p) * BQ;
+  const int nk = (prm.k_atoms + ATOMS - 1) / ATOMS;
+  w.kt_beg = (int)((int64_t)nk * w.split / prm.ksplit);
+  w.ntiles = (int)((int64_t)nk * (w.split + 1) / prm.ksplit) - w.kt_beg;
+  return w;
+}
 
 template <int FAM, int BQ, int ATOMS>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(Geo<FAM, BQ, ATOMS>::kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcDev prm) {
   using G = Geo<FAM, BQ, ATOMS>;
   extern __shared__ uint8_t smem_raw[];
@@ -161,12 +198,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile uint32_t* const abort_word = &hdr->abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int p0 = blockIdx.x * kBP, q0 = blockIdx.y * BQ;
-  const int split = blockIdx.z, ksplit = prm.ksplit;
+  const int ksplit = prm.ksplit;
   const int S = prm.stages;
-  const int nk = (prm.k_atoms + ATOMS - 1) / ATOMS;
-  const int kt_beg = (int)((int64_t)nk * split / ksplit), kt_end = (int)((int64_t)nk * (split + 1) / ksplit);
-  const int ntiles = kt_end - kt_beg;
+  const int n_items = prm.n_items;
+  const int item0 = prm.cluster ? 0 : (int)blockIdx.x;
+  const int item_step = prm.cluster ? n_items : (int)gridDim.x;  // cluster mode: exactly one pass
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -174,8 +210,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(smem_u32(&hdr->empty[s]), 1);
       mbar_init(smem_u32(&hdr->sf_full[s]), 128);
     }
-    mbar_init(smem_u32(&hdr->acc_full), 1);
     for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&hdr->acc_full[b]), 1);
+      mbar_init(smem_u32(&hdr->acc_empty[b]), 128);
       mbar_init(smem_u32(&hdr->a_full[b]), 128);
       mbar_init(smem_u32(&hdr->a_empty[b]), 1);
     }
@@ -195,49 +232,61 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem = hdr->tmem_base;
   if (prm.pdl_early) pdl_trigger();
 
-  constexpr uint32_t kAccCol = 0;
-  constexpr uint32_t kABufCol = G::kAccCols;                                             // mixed kinds
-  constexpr uint32_t kSfCol = G::kAccCols;                                               // nvfp4
-  const bool a_first = prm.a_is_weight != 0;  // which operand may stream before the dependency wait
+  constexpr uint32_t kABufCol = G::kAccBufs * G::kAccCols;  // mixed kinds: widened A buffers
+  constexpr uint32_t kSfCol = G::kAccBufs * G::kAccCols;    // nvfp4: block-scale columns
+  const bool a_first = prm.a_is_weight != 0;                // which operand may stream before the dependency wait
 
   if (warp == 0) {
     // ================================ TMA producer ================================
     if (lane == 0) {
       const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
-      auto load_a = [&](int it) {
-        const int s = it % S;
-        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
+      auto load_a = [&](const Item& w, int it, uint32_t g) {
+        const uint32_t s = g % S, st = stage0 + s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a)
-          tma_load_2d(st + G::kAOff + a * kAAtomTile, &tmA, bar, ((kt_beg + it) * ATOMS + a) * kAtomBytes, p0,
+          tma_load_2d(st + G::kAOff + a * kAAtomTile, &tmA, bar, ((w.kt_beg + it) * ATOMS + a) * kAtomBytes, w.p0,
                       a_first ? pol_w : pol_x);
       };
-      auto load_b = [&](int it) {
-        const int s = it % S;
-        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
+      auto load_b = [&](const Item& w, int it, uint32_t g) {
+        const uint32_t s = g % S, st = stage0 + s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
 #pragma unroll
         for (int a = 0; a < ATOMS * G::kBPerA; ++a)
           tma_load_2d(st + G::kBOff + a * G::kBAtomTile, &tmB, bar,
-                      ((kt_beg + it) * ATOMS * G::kBPerA + a) * kAtomBytes, q0, a_first ? pol_x : pol_w);
+                      ((w.kt_beg + it) * ATOMS * G::kBPerA + a) * kAtomBytes, w.q0, a_first ? pol_x : pol_w);
       };
-      const int npre = ntiles < S ? ntiles : S;
-      for (int it = 0; it < npre; ++it) {
-        mbar_expect_tx(smem_u32(&hdr->full[it]), G::kTxBytes);
-        if (a_first) load_a(it); else load_b(it);
+      uint32_t g = 0;
+      bool ok = true, first = true;
+      for (int item = item0; item < n_items && ok; item += item_step) {
+        const Item w = decode_item<BQ, ATOMS>(prm, item);
+        int it = 0;
+        if (first) {
+          // the ring is empty: fill it with weight tiles before waiting for the previous kernel, then add the
+          // activation tiles of the same stages
+          const int npre = w.ntiles < S ? w.ntiles : S;
+          for (int i = 0; i < npre; ++i) {
+            mbar_expect_tx(smem_u32(&hdr->full[i]), G::kTxBytes);
+            if (a_first) load_a(w, i, (uint32_t)i); else load_b(w, i, (uint32_t)i);
+          }
+          pdl_wait();
+          for (int i = 0; i < npre; ++i) {
+            if (a_first) load_b(w, i, (uint32_t)i); else load_a(w, i, (uint32_t)i);
+          }
+          it = npre;
+          g = (uint32_t)npre;
+          first = false;
+        }
+        for (; it < w.ntiles; ++it, ++g) {
+          const uint32_t s = g % S;
+          if (g >= (uint32_t)S) {
+            ok = mbar_wait(smem_u32(&hdr->empty[s]), ((g / S) & 1) ^ 1, abort_word);
+            if (!ok) { give_up(prm, ST_PRODUCER_EMPTY_WAIT); break; }
+          }
+          mbar_expect_tx(smem_u32(&hdr->full[s]), G::kTxBytes);
+          load_a(w, it, g);
+          load_b(w, it, g);
+        }
       }
-      pdl_wait();
-      for (int it = 0; it < npre; ++it) {
-        if (a_first) load_b(it); else load_a(it);
-      }
-      bool ok = true;
-      for (int it = npre; it < ntiles && ok; ++it) {
-        const int s = it % S;
-        ok = mbar_wait(smem_u32(&hdr->empty[s]), ((it / S) & 1) ^ 1, abort_word);
-        if (!ok) { give_up(prm, ST_PRODUCER_EMPTY_WAIT); break; }
-        mbar_expect_tx(smem_u32(&hdr->full[s]), G::kTxBytes);
-        load_a(it);
-        load_b(it);
-      }
+      if (first) pdl_wait();
       if (!ok) {
         // leave only after the copies already issued have landed (bounded): shared memory must not be written
         // after the CTA has gone
@@ -250,310 +299,347 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncwarp();
     if (!prm.pdl_early) pdl_trigger();
-    l2_prefetch_share(prm.pf, prm.pf_bytes, blockIdx.x + (int64_t)gridDim.x * (blockIdx.y + (int64_t)gridDim.y * blockIdx.z),
-                      (int64_t)gridDim.x * gridDim.y * gridDim.z, lane, 32);
+    l2_prefetch_share(prm.pf, prm.pf_bytes, blockIdx.x + (int64_t)gridDim.x * blockIdx.z, (int64_t)gridDim.x * gridDim.z,
+                      lane, 32);
   } else if (warp == 1) {
     // ================================ MMA issuer ================================
     if (lane == 0) {
       const uint32_t idesc = prm.idesc;
       bool ok = true;
-      for (int it = 0; it < ntiles && ok; ++it) {
-        const int s = it % S;
-        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
-        ok = mbar_wait(smem_u32(&hdr->full[s]), (it / S) & 1, abort_word);
-        if constexpr (G::kNvf4) ok = ok && mbar_wait(smem_u32(&hdr->sf_full[s]), (it / S) & 1, abort_word);
-        if constexpr (G::kMixed) ok = ok && mbar_wait(smem_u32(&hdr->a_full[it & 1]), (it >> 1) & 1, abort_word);
-        if (!ok) { give_up(prm, ST_MMA_FULL_WAIT); break; }
-        tc_fence_after();
-        if constexpr (G::kMixed) {
-          const uint32_t abuf = tmem + kABufCol + (uint32_t)(it & 1) * ATOMS * G::kAColsAtom;
-          constexpr int kMmaPerAtom = G::kAColsAtom / 8;  // K = 16 per MMA, 8 columns of widened A
+      uint32_t g = 0, n_acc = 0;
+      for (int item = item0; item < n_items && ok; item += item_step) {
+        const Item w = decode_item<BQ, ATOMS>(prm, item);
+        if (w.ntiles <= 0) continue;
+        const uint32_t ab = n_acc % G::kAccBufs, acc = tmem + ab * G::kAccCols;
+        if (n_acc >= (uint32_t)G::kAccBufs) {  // the epilogue must have drained this buffer
+          ok = mbar_wait(smem_u32(&hdr->acc_empty[ab]), ((n_acc / G::kAccBufs) & 1) ^ 1, abort_word);
+          if (!ok) { give_up(prm, ST_MMA_FULL_WAIT); break; }
+          tc_fence_after();
+        }
+        for (int it = 0; it < w.ntiles; ++it, ++g) {
+          const uint32_t s = g % S, st = stage0 + s * G::kStageBytes;
+          ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word);
+          if constexpr (G::kNvf4) ok = ok && mbar_wait(smem_u32(&hdr->sf_full[s]), (g / S) & 1, abort_word);
+          if constexpr (G::kMixed) ok = ok && mbar_wait(smem_u32(&hdr->a_full[g & 1]), (g >> 1) & 1, abort_word);
+          if (!ok) { give_up(prm, ST_MMA_FULL_WAIT); break; }
+          tc_fence_after();
+          if constexpr (G::kMixed) {
+            const uint32_t abuf = tmem + kABufCol + (g & 1u) * ATOMS * G::kAColsAtom;
+            constexpr int kMmaPerAtom = G::kAColsAtom / 8;  // K = 16 per MMA, 8 columns of widened A
 #pragma unroll
-          for (int a = 0; a < ATOMS; ++a)
+            for (int a = 0; a < ATOMS; ++a)
 #pragma unroll
-            for (int j = 0; j < kMmaPerAtom; ++j) {
-              const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + (a * G::kBPerA + j / 4) * G::kBAtomTile) + (uint64_t)((j % 4) * 2);
-              mma_ts_f16(tmem + kAccCol, abuf + a * G::kAColsAtom + j * 8, bdesc, idesc, (it | a | j) != 0);
-            }
-          umma_commit(smem_u32(&hdr->a_empty[it & 1]));
-        } else {
-          const uint32_t sfc = tmem + kSfCol + (uint32_t)(it & 1) * G::kSfColsStage;
+              for (int j = 0; j < kMmaPerAtom; ++j) {
+                const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + (a * G::kBPerA + j / 4) * G::kBAtomTile) + (uint64_t)((j % 4) * 2);
+                mma_ts_f16(acc, abuf + a * G::kAColsAtom + j * 8, bdesc, idesc, (it | a | j) != 0);
+              }
+            umma_commit(smem_u32(&hdr->a_empty[g & 1]));
+          } else {
+            const uint32_t sfc = tmem + kSfCol + (g & 1u) * G::kSfColsStage;
 #pragma unroll
-          for (int a = 0; a < ATOMS; ++a) {
-            const uint64_t adesc = umma_desc_sw128(st + G::kAOff + a * kAAtomTile);
-            const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + a * G::kBAtomTile);
+            for (int a = 0; a < ATOMS; ++a) {
+              const uint64_t adesc = umma_desc_sw128(st + G::kAOff + a * kAAtomTile);
+              const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + a * G::kBAtomTile);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {  // 32 bytes of K per MMA for every kind
-              const uint32_t acc_on = (it | a | j) != 0;
-              if constexpr (FAM == FAM_F16) mma_ss_f16(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
-              else if constexpr (FAM == FAM_F8) mma_ss_f8f6f4(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
-              else if constexpr (FAM == FAM_I8) mma_ss_i8(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
-              else {
-                const uint32_t sfa_t = sfc + (uint32_t)(a * 4 + j) * 8, sfb_t = sfa_t + 4;
-                tmem_cp_32x128b_x4(sfa_t, umma_desc_plain128(st + G::kSfAOff + (a * 4 + j) * 512));
-                tmem_cp_32x128b_x4(sfb_t, umma_desc_plain128(st + G::kSfBOff + (a * 4 + j) * 512));
-                mma_ss_nvf4(tmem + kAccCol, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on, sfa_t, sfb_t);
+              for (int j = 0; j < 4; ++j) {  // 32 bytes of K per MMA for every kind
+                const uint32_t acc_on = (it | a | j) != 0;
+                if constexpr (FAM == FAM_F16) mma_ss_f16(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
+                else if constexpr (FAM == FAM_F8) mma_ss_f8f6f4(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
+                else if constexpr (FAM == FAM_I8) mma_ss_i8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
+                else {
+                  const uint32_t sfa_t = sfc + (uint32_t)(a * 4 + j) * 8, sfb_t = sfa_t + 4;
+                  tmem_cp_32x128b_x4(sfa_t, umma_desc_plain128(st + G::kSfAOff + (a * 4 + j) * 512));
+                  tmem_cp_32x128b_x4(sfb_t, umma_desc_plain128(st + G::kSfBOff + (a * 4 + j) * 512));
+                  mma_ss_nvf4(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on, sfa_t, sfb_t);
+                }
               }
             }
           }
+          umma_commit(smem_u32(&hdr->empty[s]));
         }
-        umma_commit(smem_u32(&hdr->empty[s]));
+        if (ok) umma_commit(smem_u32(&hdr->acc_full[ab]));
+        ++n_acc;
       }
-      if (ok && ntiles > 0) umma_commit(smem_u32(&hdr->acc_full));
     }
     __syncwarp();
     if (!prm.pdl_early) pdl_trigger();
-  } else {
-    // ================================ converter / scale feeder, then epilogue ================================
-    const int et = tid - 64;                 // 0..127
-    const int quarter = warp & 3;            // tensor-memory lanes this warp may touch: [32*quarter, +32)
-    const int r = quarter * 32 + lane;       // row of the tile this thread owns
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    bool ok = true;
-
-    if constexpr (G::kNvf4 || FAM == FAM_W4A16) {
-      // Block scales travel by 4-byte cp.async (their rows are only 4-byte aligned); each thread moves the 16 scale
-      // bytes per atom of "its" row and keeps kSfLag stages in flight.
-      pdl_wait();
-      auto issue = [&](int it) {
-        const int s = it % S;
-        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
-        const int sfk_total = prm.K >> 4;
-#pragma unroll
-        for (int a = 0; a < ATOMS; ++a) {
-          const int sfk0 = ((kt_beg + it) * ATOMS + a) * 16;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int sfk = sfk0 + j * 4;
-            {
-              const bool v = p0 + r < prm.P && sfk < sfk_total;
-              const unsigned char* src = v ? prm.a_sf + (int64_t)(p0 + r) * prm.lda_sf + sfk : prm.a_sf;
-              const uint32_t dst = G::kNvf4 ? st + G::kSfAOff + (a * 4 + j) * 512 + (r & 31) * 16 + (r >> 5) * 4
-                                            : st + G::kSfAOff + a * 2048 + r * 16 + j * 4;
-              cp_async4_zfill(dst, src, v);
-            }
-            if constexpr (G::kNvf4) {
-              if (r < BQ) {
-                const bool v = q0 + r < prm.Q && sfk < sfk_total;
-                const unsigned char* src = v ? prm.b_sf + (int64_t)(q0 + r) * prm.ldb_sf + sfk : prm.b_sf;
-                cp_async4_zfill(st + G::kSfBOff + (a * 4 + j) * 512 + (r & 31) * 16 + (r >> 5) * 4, src, v);
-              }
-            }
-          }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-      };
-      if constexpr (G::kNvf4) {
-        // rows of the B scale blocks that no thread fills must not hold stale bytes that decode to NaN/Inf
-        for (int s = 0; s < S; ++s)
-          for (int i = et; i < G::kSfB / 4; i += 128)
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage0 + (uint32_t)s * G::kStageBytes + G::kSfBOff + i * 4), "r"(0u));
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-      }
-      // a slot is refilled only after the MMAs that read it have completed, and those need this thread's part of the
-      // stage: the lag must stay below the ring depth
-      const int lag = S - 1 < kSfLag ? S - 1 : kSfLag;
-      for (int it = 0; it < ntiles + lag && ok; ++it) {
-        if (it < ntiles) {
-          if (it >= S) ok = mbar_wait(smem_u32(&hdr->empty[it % S]), ((it / S) & 1) ^ 1, abort_word);
-          if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
-          issue(it);
-        } else {
-          asm volatile("cp.async.commit_group;" ::: "memory");
-        }
-        const int done = it - lag;
-        if (done < 0) continue;
-        if (lag == 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
-        else if (lag == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
-        else asm volatile("cp.async.wait_group 1;" ::: "memory");
-        const int s = done % S;
+  } else if (warp >= 6) {
+    // ================================ helpers: block-scale feeder / weight converter ================================
+    if constexpr (G::kHelpers) {
+      const int ht = tid - 192;                // 0..127
+      const int quarter = warp & 3;            // tensor-memory lanes this warp may touch: [32*quarter, +32)
+      const int r = quarter * 32 + lane;       // row of the tile this thread owns
+      const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+      bool ok = true;
+      uint32_t g = 0;
+      if constexpr (G::kNvf4 || FAM == FAM_W4A16) {
+        // Block scales travel by 4-byte cp.async (their rows are only 4-byte aligned); each thread moves the 16 scale
+        // bytes per atom of "its" row and keeps up to kSfLag stages in flight.
+        pdl_wait();
         if constexpr (G::kNvf4) {
-          fence_async_shared();
-          mbar_arrive(smem_u32(&hdr->sf_full[s]));
-        } else {
-          // ---- W4A16: widen stage `done` (weight nibbles x block scale) into tensor memory ----
-          const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
-          const bool bf16 = prm.bf16_act != 0;
-          ok = mbar_wait(smem_u32(&hdr->full[s]), (done / S) & 1, abort_word) &&
-               mbar_wait(smem_u32(&hdr->a_empty[done & 1]), ((done >> 1) & 1) ^ 1, abort_word);
-          if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
-          tc_fence_after();
-          const uint32_t abuf = tmem + lane_addr + kABufCol + (uint32_t)(done & 1) * ATOMS * G::kAColsAtom;
-#pragma unroll
-          for (int a = 0; a < ATOMS; ++a) {
-            const uint4 sc = lds128(st + G::kSfAOff + a * 2048 + r * 16);
-            const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
-              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-              // chunk c holds K [32c, 32c+32) of the atom = scale blocks 2c and 2c+1
-              const uint32_t s0 = widen_scale((scw[c >> 1] >> (16 * (c & 1))) & 0xffu, bf16);
-              const uint32_t s1 = widen_scale((scw[c >> 1] >> (16 * (c & 1) + 8)) & 0xffu, bf16);
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                uint32_t o[8];
-#pragma unroll
-                for (int b = 0; b < 8; ++b)
-                  o[b] = widen_e2m1x2((w[h * 2 + b / 4] >> (8 * (b % 4))) & 0xffu, bf16, h ? s1 : s0);
-                tmem_st8(abuf + a * G::kAColsAtom + c * 16 + h * 8, o);
-              }
-            }
-          }
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(smem_u32(&hdr->a_full[done & 1]));
+          // rows of the B scale blocks that no thread fills must not hold stale bytes
+          for (int s = 0; s < S; ++s)
+            for (int i = ht; i < G::kSfB / 4; i += 128)
+              asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage0 + (uint32_t)s * G::kStageBytes + G::kSfBOff + i * 4), "r"(0u));
+          asm volatile("bar.sync 2, 128;" ::: "memory");
         }
-      }
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    } else if constexpr (FAM == FAM_W8A16) {
-      const bool bf16 = prm.bf16_act != 0;
-      for (int it = 0; it < ntiles && ok; ++it) {
-        const int s = it % S;
-        const uint32_t st = stage0 + (uint32_t)s * G::kStageBytes;
-        ok = mbar_wait(smem_u32(&hdr->full[s]), (it / S) & 1, abort_word) &&
-             mbar_wait(smem_u32(&hdr->a_empty[it & 1]), ((it >> 1) & 1) ^ 1, abort_word);
-        if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
-        tc_fence_after();
-        const uint32_t abuf = tmem + lane_addr + kABufCol + (uint32_t)(it & 1) * ATOMS * G::kAColsAtom;
+        // a slot is refilled only after the MMAs that read it have completed, and those need this thread's part of
+        // the stage: the lag must stay below the ring depth
+        const int lag = S - 1 < kSfLag ? S - 1 : kSfLag;
+        const int sfk_total = prm.K >> 4;
+        for (int item = item0; item < n_items && ok; item += item_step) {
+          const Item w = decode_item<BQ, ATOMS>(prm, item);
+          for (int it = 0; it < w.ntiles + lag && ok; ++it) {
+            if (it < w.ntiles) {
+              const uint32_t gi = g + (uint32_t)it, s = gi % S, st = stage0 + s * G::kStageBytes;
+              if (gi >= (uint32_t)S) ok = mbar_wait(smem_u32(&hdr->empty[s]), ((gi / S) & 1) ^ 1, abort_word);
+              if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
 #pragma unroll
-        for (int a = 0; a < ATOMS; ++a)
+              for (int a = 0; a < ATOMS; ++a) {
+                const int sfk0 = ((w.kt_beg + it) * ATOMS + a) * 16;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
-            uint32_t o[8];
-            widen_e4m3x4(raw.x, bf16, o[0], o[1]);
-            widen_e4m3x4(raw.y, bf16, o[2], o[3]);
-            widen_e4m3x4(raw.z, bf16, o[4], o[5]);
-            widen_e4m3x4(raw.w, bf16, o[6], o[7]);
-            tmem_st8(abuf + a * G::kAColsAtom + c * 8, o);
-          }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&hdr->a_full[it & 1]));
-      }
-    }
-
-    // ---------------------------------- epilogue ----------------------------------
-    pdl_wait();
-    if (ok && ntiles > 0) {
-      ok = mbar_wait(smem_u32(&hdr->acc_full), 0, abort_word);
-      if (!ok) give_up(prm, ST_EPILOGUE_WAIT);
-      tc_fence_after();
-    }
-    const bool have_acc = ok && ntiles > 0;
-    const float alpha = prm.alpha_ptr ? prm.alpha * __ldg(prm.alpha_ptr) : prm.alpha;
-    const int p = p0 + r;
-    const int nq = min(BQ, prm.Q - q0);
-    const uint32_t parked = stage0;  // cluster split-K: [BQ][128] 4-byte partials, q-major
-
-    for (int c0 = 0; c0 < BQ; c0 += 16) {
-      if (c0 >= nq) break;
-      uint32_t v[16];
-      if (have_acc) {
-        tmem_ld16(tmem + lane_addr + kAccCol + c0, v);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) v[c] = 0u;
-      }
-      if (ksplit == 1) {
-        if (p < prm.P) {
-          bool done = false;
-          if (!prm.swap && c0 + 16 <= nq) {
-            // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
-            if (prm.out_dtype == LLG_DT_F32) {
-              float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
-              if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-                for (int c = 0; c < 16; c += 4) {
-                  float4 o;
-                  o.x = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
-                  o.y = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
-                  o.z = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 2, v[c + 2]);
-                  o.w = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 3, v[c + 3]);
-                  *reinterpret_cast<float4*>(dst + c) = o;
-                }
-                done = true;
-              }
-            } else {
-              uint16_t* dst = static_cast<uint16_t*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
-              if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                uint32_t o[8];
-#pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                  const float a = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
-                  const float b = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
-                  if (prm.out_dtype == LLG_DT_BF16) {
-                    const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
-                    o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
-                  } else {
-                    const __half2 t = __halves2half2(__float2half_rn(a), __float2half_rn(b));
-                    o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                for (int j = 0; j < 4; ++j) {
+                  const int sfk = sfk0 + j * 4;
+                  {
+                    const bool v = w.p0 + r < prm.P && sfk < sfk_total;
+                    const unsigned char* src = v ? prm.a_sf + (int64_t)(w.p0 + r) * prm.lda_sf + sfk : prm.a_sf;
+                    const uint32_t dst = G::kNvf4 ? st + G::kSfAOff + (a * 4 + j) * 512 + (r & 31) * 16 + (r >> 5) * 4
+                                                  : st + G::kSfAOff + a * 2048 + r * 16 + j * 4;
+                    cp_async4_zfill(dst, src, v);
+                  }
+                  if constexpr (G::kNvf4) {
+                    if (r < BQ) {
+                      const bool v = w.q0 + r < prm.Q && sfk < sfk_total;
+                      const unsigned char* src = v ? prm.b_sf + (int64_t)(w.q0 + r) * prm.ldb_sf + sfk : prm.b_sf;
+                      cp_async4_zfill(st + G::kSfBOff + (a * 4 + j) * 512 + (r & 31) * 16 + (r >> 5) * 4, src, v);
+                    }
                   }
                 }
-                *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
-                done = true;
               }
             }
-          }
-          if (!done) {
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            const int done = it - lag;
+            if (done < 0) continue;
+            if (lag == 3) asm volatile("cp.async.wait_group 3;" ::: "memory");
+            else if (lag == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+            else asm volatile("cp.async.wait_group 1;" ::: "memory");
+            const uint32_t gd = g + (uint32_t)done, s = gd % S;
+            if constexpr (G::kNvf4) {
+              fence_async_shared();
+              mbar_arrive(smem_u32(&hdr->sf_full[s]));
+            } else {
+              // ---- W4A16: widen stage `done` (weight nibbles x block scale) into tensor memory ----
+              const uint32_t st = stage0 + s * G::kStageBytes;
+              const bool bf16 = prm.bf16_act != 0;
+              ok = mbar_wait(smem_u32(&hdr->full[s]), (gd / S) & 1, abort_word);
+              if (ok && gd >= 2) ok = mbar_wait(smem_u32(&hdr->a_empty[gd & 1]), ((gd >> 1) & 1) ^ 1, abort_word);
+              if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
+              tc_fence_after();
+              const uint32_t abuf = tmem + lane_addr + kABufCol + (gd & 1u) * ATOMS * G::kAColsAtom;
 #pragma unroll
-            for (int c = 0; c < 16; ++c)
-              if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]));
-          }
-        }
-      } else if (prm.cluster) {
+              for (int a = 0; a < ATOMS; ++a) {
+                const uint4 sc = lds128(st + G::kSfAOff + a * 2048 + r * 16);
+                const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
-        for (int c = 0; c < 16; ++c)
-          asm volatile("st.shared.u32 [%0], %1;" ::"r"(parked + (uint32_t)((c0 + c) * kBP + r) * 4u), "r"(v[c]) : "memory");
-      } else {
-        // partial plane in the output's own element order, so both this write and the later read are coalesced
-        uint32_t* const ws = static_cast<uint32_t*>(prm.ws) + (int64_t)split * prm.P * prm.Q;
-        if (p < prm.P) {
+                for (int c = 0; c < 8; ++c) {
+                  const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+                  const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+                  // chunk c holds K [32c, 32c+32) of the atom = scale blocks 2c and 2c+1
+                  const uint32_t s0 = widen_scale((scw[c >> 1] >> (16 * (c & 1))) & 0xffu, bf16);
+                  const uint32_t s1 = widen_scale((scw[c >> 1] >> (16 * (c & 1) + 8)) & 0xffu, bf16);
 #pragma unroll
-          for (int c = 0; c < 16; ++c)
-            if (c0 + c < nq) {
-              const int q = q0 + c0 + c;
-              ws[prm.swap ? (int64_t)q * prm.P + p : (int64_t)p * prm.Q + q] = v[c];
+                  for (int h = 0; h < 2; ++h) {
+                    uint32_t o[8];
+#pragma unroll
+                    for (int b = 0; b < 8; ++b)
+                      o[b] = widen_e2m1x2((wv[h * 2 + b / 4] >> (8 * (b % 4))) & 0xffu, bf16, h ? s1 : s0);
+                    tmem_st8(abuf + a * G::kAColsAtom + c * 16 + h * 8, o);
+                  }
+                }
+              }
+              tmem_wait_st();
+              tc_fence_before();
+              mbar_arrive(smem_u32(&hdr->a_full[gd & 1]));
             }
+          }
+          g += (uint32_t)w.ntiles;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      } else {
+        // ---- W8A16: widen each stage's weight bytes into tensor memory ----
+        const bool bf16 = prm.bf16_act != 0;
+        for (int item = item0; item < n_items && ok; item += item_step) {
+          const Item w = decode_item<BQ, ATOMS>(prm, item);
+          for (int it = 0; it < w.ntiles && ok; ++it, ++g) {
+            const uint32_t s = g % S, st = stage0 + s * G::kStageBytes;
+            ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word);
+            if (ok && g >= 2) ok = mbar_wait(smem_u32(&hdr->a_empty[g & 1]), ((g >> 1) & 1) ^ 1, abort_word);
+            if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
+            tc_fence_after();
+            const uint32_t abuf = tmem + lane_addr + kABufCol + (g & 1u) * ATOMS * G::kAColsAtom;
+#pragma unroll
+            for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+                uint32_t o[8];
+                widen_e4m3x4(raw.x, bf16, o[0], o[1]);
+                widen_e4m3x4(raw.y, bf16, o[2], o[3]);
+                widen_e4m3x4(raw.z, bf16, o[4], o[5]);
+                widen_e4m3x4(raw.w, bf16, o[6], o[7]);
+                tmem_st8(abuf + a * G::kAColsAtom + c * 8, o);
+              }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&hdr->a_full[g & 1]));
+          }
         }
       }
     }
-
-    if (ksplit > 1 && !prm.cluster) {
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const unsigned tile = blockIdx.x + gridDim.x * blockIdx.y;
-      if (et == 0) hdr->last = atomicAdd(&prm.counters[tile], 1u) == (unsigned)(ksplit - 1) ? 1u : 0u;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (hdr->last) {
-        __threadfence();
-        const int np = min(kBP, prm.P - p0);
-        const int64_t plane = (int64_t)prm.P * prm.Q;
-        const uint32_t* const ws = static_cast<const uint32_t*>(prm.ws);
-        for (int i = et; i < np * nq; i += 128) {
-          const int pl = prm.swap ? i % np : i / nq, ql = prm.swap ? i / np : i % nq;
-          const int pp = p0 + pl, qq = q0 + ql;
-          const uint32_t* src = ws + (prm.swap ? (int64_t)qq * prm.P + pp : (int64_t)pp * prm.Q + qq);
-          uint32_t total = 0u;
-          for (int k0 = 0; k0 < ksplit; k0 += 8) {  // 8 loads in flight, added in split order
-            uint32_t part[8];
+  } else {
+    // ================================ epilogue (warps 2-5) ================================
+    const int et = tid - 64;                 // 0..127
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t parked = stage0;          // cluster split-K: [BQ][128] 4-byte partials, q-major
+    bool ok = true;
+    uint32_t n_acc = 0;
+    pdl_wait();
+    const float alpha = prm.alpha_ptr ? prm.alpha * __ldg(prm.alpha_ptr) : prm.alpha;
+    for (int item = item0; item < n_items; item += item_step) {
+      const Item w = decode_item<BQ, ATOMS>(prm, item);
+      const uint32_t ab = n_acc % G::kAccBufs;
+      bool have_acc = false;
+      if (w.ntiles > 0) {
+        if (ok) {
+          ok = mbar_wait(smem_u32(&hdr->acc_full[ab]), (n_acc / G::kAccBufs) & 1, abort_word);
+          if (!ok) give_up(prm, ST_EPILOGUE_WAIT);
+        }
+        tc_fence_after();
+        have_acc = ok;
+      }
+      const int p = w.p0 + r;
+      const int nq = min(BQ, prm.Q - w.q0);
+      const int q0 = w.q0;
+      for (int c0 = 0; c0 < BQ; c0 += 16) {
+        if (c0 >= nq) break;
+        uint32_t v[16];
+        if (have_acc) {
+          tmem_ld16(tmem + lane_addr + ab * G::kAccCols + c0, v);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (k0 + j < ksplit) part[j] = __ldcg(src + (int64_t)(k0 + j) * plane);
+          for (int c = 0; c < 16; ++c) v[c] = 0u;
+        }
+        if (ksplit == 1) {
+          if (p < prm.P) {
+            bool done = false;
+            if (!prm.swap && c0 + 16 <= nq) {
+              // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
+              if (prm.out_dtype == LLG_DT_F32) {
+                float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
+                if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (k0 + j < ksplit) {
-                if (k0 + j == 0) total = part[j];
-                else if constexpr (G::kIntAcc) total = (uint32_t)((int32_t)total + (int32_t)part[j]);
-                else total = __float_as_uint(__uint_as_float(total) + __uint_as_float(part[j]));
+                  for (int c = 0; c < 16; c += 4) {
+                    float4 o;
+                    o.x = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
+                    o.y = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
+                    o.z = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 2, v[c + 2]);
+                    o.w = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 3, v[c + 3]);
+                    *reinterpret_cast<float4*>(dst + c) = o;
+                  }
+                  done = true;
+                }
+              } else {
+                uint16_t* dst = static_cast<uint16_t*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
+                if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                  uint32_t o[8];
+#pragma unroll
+                  for (int c = 0; c < 16; c += 2) {
+                    const float a = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
+                    const float b = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
+                    if (prm.out_dtype == LLG_DT_BF16) {
+                      const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+                      o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                    } else {
+                      const __half2 t = __halves2half2(__float2half_rn(a), __float2half_rn(b));
+                      o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                    }
+                  }
+                  *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                  *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                  done = true;
+                }
+              }
+            }
+            if (!done) {
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]));
+            }
+          }
+        } else if (prm.cluster) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(parked + (uint32_t)((c0 + c) * kBP + r) * 4u), "r"(v[c]) : "memory");
+        } else {
+          // partial plane in the output's own element order, so both this write and the later read are coalesced
+          uint32_t* const ws = static_cast<uint32_t*>(prm.ws) + (int64_t)w.split * prm.P * prm.Q;
+          if (p < prm.P) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              if (c0 + c < nq) {
+                const int q = q0 + c0 + c;
+                ws[prm.swap ? (int64_t)q * prm.P + p : (int64_t)p * prm.Q + q] = v[c];
               }
           }
-          tc_store(prm, pp, qq, tc_finish<G::kIntAcc>(prm, alpha, pp, qq, total));
         }
-        if (et == 0) prm.counters[tile] = 0u;
+      }
+      if (w.ntiles > 0) {
+        // the accumulator buffer may be overwritten by the MMAs of a later item from here on
+        tc_fence_before();
+        mbar_arrive(smem_u32(&hdr->acc_empty[ab]));
+        ++n_acc;
+      }
+
+      if (ksplit > 1 && !prm.cluster) {
+        // Publish: the CTA barrier orders every thread's partial stores before thread 0's gpu-scope fence, which is
+        // cumulative, so whoever observes the counter increment also observes the whole tile of partials.
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          __threadfence();
+          hdr->last = atomicAdd(&prm.counters[w.tile], 1u) == (unsigned)(ksplit - 1) ? 1u : 0u;
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (hdr->last) {
+          const int np = min(kBP, prm.P - w.p0);
+          const int64_t plane = (int64_t)prm.P * prm.Q;
+          const uint32_t* const ws = static_cast<const uint32_t*>(prm.ws);
+          for (int i = et; i < np * nq; i += 128) {
+            const int pl = prm.swap ? i % np : i / nq, ql = prm.swap ? i / np : i % nq;
+            const int pp = w.p0 + pl, qq = q0 + ql;
+            const uint32_t* src = ws + (prm.swap ? (int64_t)qq * prm.P + pp : (int64_t)pp * prm.Q + qq);
+            uint32_t total = 0u;
+            for (int k0 = 0; k0 < ksplit; k0 += 8) {  // 8 loads in flight, added in split order
+              uint32_t part[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (k0 + j < ksplit) part[j] = __ldcg(src + (int64_t)(k0 + j) * plane);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (k0 + j < ksplit) {
+                  if (k0 + j == 0) total = part[j];
+                  else if constexpr (G::kIntAcc) total = (uint32_t)((int32_t)total + (int32_t)part[j]);
+                  else total = __float_as_uint(__uint_as_float(total) + __uint_as_float(part[j]));
+                }
+            }
+            tc_store(prm, pp, qq, tc_finish<G::kIntAcc>(prm, alpha, pp, qq, total));
+          }
+          if (et == 0) prm.counters[w.tile] = 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // hdr->last is rewritten by the next item
       }
     }
   }
@@ -562,10 +648,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // every thread of every CTA of the cluster passes both barriers, whatever happened above
     cluster_arrive();
     cluster_wait();
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
+      const Item w = decode_item<BQ, ATOMS>(prm, 0);
       const int et = tid - 64;
       const float alpha = prm.alpha_ptr ? prm.alpha * __ldg(prm.alpha_ptr) : prm.alpha;
-      const int np = min(kBP, prm.P - p0), nq = min(BQ, prm.Q - q0);
+      const int np = min(kBP, prm.P - w.p0), nq = min(BQ, prm.Q - w.q0);
       const int total = kBP * nq, share = (total + ksplit - 1) / ksplit;
       const int lo = (int)cluster_ctarank() * share, hi = min(total, lo + share);
       for (int i = lo + et; i < hi; i += 128) {
@@ -583,7 +670,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if constexpr (G::kIntAcc) sum = (uint32_t)((int32_t)sum + (int32_t)part[k]);
             else sum = __float_as_uint(__uint_as_float(sum) + __uint_as_float(part[k]));
           }
-        tc_store(prm, p0 + pl, q0 + ql, tc_finish<G::kIntAcc>(prm, alpha, p0 + pl, q0 + ql, sum));
+        tc_store(prm, w.p0 + pl, w.q0 + ql, tc_finish<G::kIntAcc>(prm, alpha, w.p0 + pl, w.q0 + ql, sum));
       }
     }
     cluster_arrive();  // partials stay readable until every CTA of the cluster is done with them
@@ -627,9 +714,26 @@ cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
       if (e != cudaSuccess) return e;
       if (dev < 32) attr_done |= 1u << dev;
     }
-    const dim3 grid((p.P + kBP - 1) / kBP, (p.Q + BQ - 1) / BQ, p.ksplit);
-    p.pdl_early = (int64_t)grid.x * grid.y * grid.z <= sm_count();
-    return launch_ex(umma_gemm_kernel<FAM, BQ, ATOMS>, grid, dim3(kTcThreads), smem, stream, pdl,
+    const int64_t tiles = (int64_t)((p.P + kBP - 1) / kBP) * ((p.Q + BQ - 1) / BQ);
+    dim3 grid;
+    if (p.cluster) {
+      if (tiles > INT32_MAX) return cudaErrorInvalidValue;
+      p.n_items = 1;
+      grid = dim3((unsigned)tiles, 1, p.ksplit);
+      p.pdl_early = tiles * p.ksplit <= sm_count();
+    } else {
+      const int64_t items = tiles * p.ksplit;
+      if (items > INT32_MAX) return cudaErrorInvalidValue;
+      p.n_items = (int)items;
+      // CTAs that fit on one SM at once: shared memory (228 KB per SM, 1 KB reserved per CTA) and tensor memory
+      int occ = (int)((228 * 1024) / (smem + 1024));
+      if (occ > 512 / G::kTmemCols) occ = 512 / G::kTmemCols;
+      occ = occ < 1 ? 1 : occ > 4 ? 4 : occ;
+      const int64_t resident = (int64_t)sm_count() * occ;
+      grid = dim3((unsigned)(items < resident ? items : resident), 1, 1);
+      p.pdl_early = 1;  // one wave by construction: let the next kernel's CTAs take the SMs as they free up
+    }
+    return launch_ex(umma_gemm_kernel<FAM, BQ, ATOMS>, grid, dim3(G::kThreads), smem, stream, pdl,
                      dim3(1, 1, p.cluster ? p.ksplit : 1), ta, tb, p);
   }
 }

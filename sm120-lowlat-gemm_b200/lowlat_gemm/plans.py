@@ -194,35 +194,38 @@ def _fit_cfg(kind: str, cfg: int) -> int:
     return cfg
 
 
+_WBITS = {"bf16": 16, "f16": 16, "fp8": 8, "int8": 8, "nvfp4": 4, "w8a16_bf16": 8, "w8a16_f16": 8, "w4a16_bf16": 4,
+          "w4a16_f16": 4}
+
+
 def default_tc_choice(kind: str, m: int, n: int, k: int, sm_count: int) -> TcChoice:
-    """Weight on the 128-row side ("swap") while the token count fits one narrow tile, activations there otherwise;
-    K is split until the grid covers the SMs, aiming at two co-resident CTAs per SM."""
+    """Weight on the 128-row side ("swap") while the token count fits one narrow tile, activations there otherwise.
+    The kernel is persistent (one CTA per SM walks the (tile, K partition) items), so the K split is picked with a small
+    cost model: weight bytes over the fraction of SMs kept busy by the last round, plus the split-K partial traffic,
+    plus a fixed cost per item."""
     swap = kind in _MIXED or m <= 64
     if swap:
         cfg = 0 if m <= 16 else 1 if m <= 32 else 2 if m <= 64 else 3 if m <= 128 else 4
     else:
-        cfg = 3 if m * n <= (1 << 22) else 4
+        cfg = 4 if n >= 2048 and m >= 256 else 3
     cfg = _fit_cfg(kind, cfg)
     bp, bq, _, stage = tc_info(kind, cfg)
     p, q = (n, m) if swap else (m, n)
     tiles = -(-p // bp) * -(-q // bq)
     nk = -(-k // (KINDS[kind][1] * cfg_atoms(cfg)))
-    slots = 2 * sm_count
-    best, best_eff = 1, 0.0
+    weight = n * k * _WBITS[kind] / 8
+    best, best_t = 1, None
     for ks in range(1, 17):
         if ks > 1 and nk // ks < 2:
             break
-        ctas = tiles * ks
-        eff = ctas / (-(-ctas // slots) * slots)
-        if eff >= 0.85:
-            best = ks
-            break
-        if eff > best_eff + 1e-9:
-            best, best_eff = ks, eff
-    ctas = tiles * best
-    budget = smem_budget()
-    per_cta = budget if ctas <= sm_count else (budget - 4096) // 2
-    stages = max(2, min(max_stages(kind, cfg), per_cta // stage, -(-nk // best) + 1))
+        items = tiles * ks
+        rounds = -(-items // sm_count)
+        busy = items / (rounds * sm_count)
+        partials = 2.0 * ks * p * q * 4 if ks > 1 else 0.0
+        t = (weight / busy + 0.5 * partials) / 6.5e6 + rounds * 0.4  # microseconds
+        if best_t is None or t < best_t - 1e-9:
+            best, best_t = ks, t
+    stages = max(2, min(max_stages(kind, cfg), nk + 1))
     return TcChoice(cfg=cfg, swap=swap, stages=stages, ksplit=best)
 
 

@@ -367,12 +367,18 @@ def test_supports_and_shapes():
 
 
 # ---------------------------------------------------------------------------------------------------------------
-# the benchmark configurations at full size: max-abs error <= 1e-2 x RMS(ref) against the fp32 host matmul
+# the benchmark configurations at full size: max-abs error <= 1e-2 x RMS(ref) against the fp32 host matmul.
+# The bound is applied to the fp32-output result. A 16-bit output is then required to be exactly that result rounded
+# to the output type: rounding a correct value to bf16 alone moves it by up to 2^-9 of its magnitude, which at the
+# largest of 44k N(0, s) outputs (4.3 s) is already 1.2e-2 x RMS, so the bound cannot be asked of a bf16 tensor.
 
 
-def _rms_ok(y, ref32):
-    err = np.abs(y.double().cpu().numpy() - ref32.astype(np.float64)).max()
-    return err <= 1e-2 * np.sqrt(np.mean(ref32.astype(np.float64) ** 2))
+def _check(call, ref32):
+    y32 = call(torch.float32)
+    err = np.abs(y32.double().cpu().numpy() - ref32.astype(np.float64)).max()
+    assert err <= 1e-2 * np.sqrt(np.mean(ref32.astype(np.float64) ** 2)), err
+    y16 = call(torch.bfloat16)
+    assert y16.dtype == torch.bfloat16 and torch.equal(y16, y32.to(torch.bfloat16))
 
 
 def test_config1_bf16():
@@ -380,9 +386,9 @@ def test_config1_bf16():
     x = torch.randn(4, 4096, generator=g).to(torch.bfloat16)
     w = (torch.randn(11008, 4096, generator=g) * 0.02).to(torch.bfloat16)
     ref = O.gemm_f32(x.float().numpy(), w.float().numpy())
-    for plan in (None, Plan(tc=L.default_plan("bf16", 11008, 4096, sms()).tc)):
-        y = L.gemm(x.to(DEV), w.to(DEV), plan=plan)
-        assert y.dtype == torch.bfloat16 and _rms_ok(y, ref)
+    xc, wc = x.to(DEV), w.to(DEV)
+    for plan in (None, Plan(tc=L.default_plan("bf16", 11008, 4096, sms()).tc)):  # skinny engine, tensor-core engine
+        _check(lambda dt: L.gemm(xc, wc, plan=plan, out_dtype=dt), ref)
 
 
 @pytest.mark.parametrize("m", [1, 16, 256])
@@ -391,13 +397,35 @@ def test_config2_fp8_and_w8a16(m):
     x = torch.randn(m, 4096, generator=g).to(torch.bfloat16)
     w_scale = (torch.rand(14336, generator=g) * 1.5 + 0.5) * 1e-3
     w = ((torch.randn(14336, 4096, generator=g) * 0.02) / w_scale[:, None]).clamp(-448, 448).to(FP8)
-    xq, xs = L.quantize_fp8(x.to(DEV))
+    xc, wc, wsc = x.to(DEV), w.to(DEV), w_scale.to(DEV)
+    xq, xs = L.quantize_fp8(xc)
     wd = O.dequant("fp8", w.view(torch.uint8).numpy()) * w_scale.double().numpy()[:, None]
     xd = O.dequant("fp8", xq.view(torch.uint8).cpu().numpy()) * xs.double().cpu().numpy()[:, None]
-    y = L.gemm(xq, w.to(DEV), x_scale=xs, w_scale=w_scale.to(DEV))
-    assert y.dtype == torch.bfloat16 and _rms_ok(y, O.gemm_f32(xd, wd))
-    y = L.gemm(x.to(DEV), w.to(DEV), w_scale=w_scale.to(DEV))
-    assert _rms_ok(y, O.gemm_f32(x.double().numpy(), wd))
+    _check(lambda dt: L.gemm(xq, wc, x_scale=xs, w_scale=wsc, out_dtype=dt), O.gemm_f32(xd, wd))
+    _check(lambda dt: L.gemm(xc, wc, w_scale=wsc, out_dtype=dt), O.gemm_f32(x.double().numpy(), wd))
+
+
+@pytest.mark.parametrize("m,ksplit", [(1, 1), (8, 4), (32, 8), (128, 4)])
+def test_config3_int8(m, ksplit):
+    g = torch.Generator().manual_seed(0)
+    xf = torch.randn(m, 4096, generator=g).to(torch.bfloat16)
+    w = torch.randint(-127, 128, (4096, 4096), generator=g, dtype=torch.int8)
+    ws = (torch.rand(4096, generator=g) + 0.5) * 1e-2
+    bias = (torch.randn(4096, generator=g) * 0.1).to(torch.bfloat16)
+    x, xs = L.quantize_int8(xf.to(DEV))
+    want = O.gemm_int8_exact(x.cpu().numpy(), w.numpy(), xs.cpu().numpy(), ws.numpy(), 1.0, bias.float().numpy())
+    c = TcChoice(cfg=0 if m <= 16 else 1 if m <= 32 else 3, swap=True, stages=6, ksplit=ksplit)
+    y = L.gemm(x, w.to(DEV), x_scale=xs, w_scale=ws.to(DEV), bias=bias.to(DEV), out_dtype=torch.float32, plan=Plan(tc={m: c}))
+    assert np.array_equal(y.cpu().numpy(), want)
+    y = L.gemm(x, w.to(DEV), x_scale=xs, w_scale=ws.to(DEV), bias=bias.to(DEV))  # the default plan, bf16 out
+    assert _close_bf16(y, want)
+
+
+def _close_bf16(y, want32):
+    """Default plans may pick the unswapped orientation, whose scale order differs by one fp32 rounding: allow one bf16 ulp."""
+    a = y.float().cpu().numpy()
+    b = torch.from_numpy(want32).to(torch.bfloat16).float().numpy()
+    return bool((np.abs(a - b) <= np.abs(b) * 2.0**-7 + 1e-30).all())
 
 
 @pytest.mark.parametrize("m", [1, 16])
@@ -407,12 +435,13 @@ def test_config4_nvfp4(m):
     wf = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
     gw = torch.tensor([448 * 6 / wf.float().abs().max().item()], device=DEV)
     wq, wsf = L.quantize_nvfp4(wf, gw)           # weights quantised with the library's own (oracle-checked) quantizer
+    del wf
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
     wd = O.dequant("fp4", wq.view(torch.uint8).cpu().numpy(), wsf.view(torch.uint8).cpu().numpy()) / float(gw.item())
-    y = L.gemm(x, wq, w_block_scale=wsf, w_scale=1.0 / gw.item())
-    assert _rms_ok(y, O.gemm_f32(x.double().cpu().numpy(), wd))
+    _check(lambda dt: L.gemm(x, wq, w_block_scale=wsf, w_scale=1.0 / gw.item(), out_dtype=dt),
+           O.gemm_f32(x.double().cpu().numpy(), wd))
     gx = torch.tensor([448 * 6 / x.float().abs().max().item()], device=DEV)
     xq, xsf = L.quantize_nvfp4(x, gx)
     xd = O.dequant("fp4", xq.view(torch.uint8).cpu().numpy(), xsf.view(torch.uint8).cpu().numpy()) / float(gx.item())
-    y = L.gemm(xq, wq, x_block_scale=xsf, w_block_scale=wsf, x_scale=1.0 / gx.item(), w_scale=1.0 / gw.item())
-    assert _rms_ok(y, O.gemm_f32(xd, wd))
+    _check(lambda dt: L.gemm(xq, wq, x_block_scale=xsf, w_block_scale=wsf, x_scale=1.0 / gx.item(), w_scale=1.0 / gw.item(),
+                             out_dtype=dt), O.gemm_f32(xd, wd))
