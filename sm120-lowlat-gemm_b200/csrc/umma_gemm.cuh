@@ -95,6 +95,14 @@ __device__ __forceinline__ float tc_finish(const TcDev& prm, float alpha, int p,
   if (prm.bias_dtype != LLG_DT_NONE) v = __fadd_rn(v, tc_bias(prm, prm.bias_on_p ? p : q));
   return v;
 }
+// Same arithmetic with the row-side factors (row scale, bias when it is indexed by p) already in registers.
+template <bool INT_ACC>
+__device__ __forceinline__ float tc_finish_row(const TcDev& prm, float alpha, float rs, float bias_p, int q, uint32_t bits) {
+  const float acc = INT_ACC ? (float)(int32_t)bits : __uint_as_float(bits);
+  float v = __fmul_rn(__fmul_rn(__fmul_rn(acc, alpha), rs), tc_vec(prm.col_scale, prm.col_scale_len, q));
+  if (prm.bias_dtype != LLG_DT_NONE) v = __fadd_rn(v, prm.bias_on_p ? bias_p : tc_bias(prm, q));
+  return v;
+}
 __device__ __forceinline__ void tc_store(const TcDev& prm, int p, int q, float v) {
   const int64_t at = prm.swap ? (int64_t)q * prm.ldy + p : (int64_t)p * prm.ldy + q;
   switch (prm.out_dtype) {
@@ -511,6 +519,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const Item w = decode_item<BQ, ATOMS>(prm, item);
       const uint32_t ab = n_acc % G::kAccBufs;
       bool have_acc = false;
+      const int p = w.p0 + r;
+      const int nq = min(BQ, prm.Q - w.q0);
+      const int q0 = w.q0;
+      // row-side epilogue operands are fetched while the MMAs still run
+      float rs = 1.f, bias_p = 0.f;
+      if (ksplit == 1 && p < prm.P) {
+        rs = tc_vec(prm.row_scale, prm.row_scale_len, p);
+        if (prm.bias_dtype != LLG_DT_NONE && prm.bias_on_p) bias_p = tc_bias(prm, p);
+      }
       if (w.ntiles > 0) {
         if (ok) {
           ok = mbar_wait(smem_u32(&hdr->acc_full[ab]), (n_acc / G::kAccBufs) & 1, abort_word);
@@ -519,9 +536,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         have_acc = ok;
       }
-      const int p = w.p0 + r;
-      const int nq = min(BQ, prm.Q - w.q0);
-      const int q0 = w.q0;
       for (int c0 = 0; c0 < BQ; c0 += 16) {
         if (c0 >= nq) break;
         uint32_t v[16];
@@ -543,10 +557,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                   for (int c = 0; c < 16; c += 4) {
                     float4 o;
-                    o.x = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
-                    o.y = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
-                    o.z = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 2, v[c + 2]);
-                    o.w = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 3, v[c + 3]);
+                    o.x = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c, v[c]);
+                    o.y = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 1, v[c + 1]);
+                    o.z = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 2, v[c + 2]);
+                    o.w = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 3, v[c + 3]);
                     *reinterpret_cast<float4*>(dst + c) = o;
                   }
                   done = true;
@@ -557,8 +571,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   uint32_t o[8];
 #pragma unroll
                   for (int c = 0; c < 16; c += 2) {
-                    const float a = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]);
-                    const float b = tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c + 1, v[c + 1]);
+                    const float a = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c, v[c]);
+                    const float b = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 1, v[c + 1]);
                     if (prm.out_dtype == LLG_DT_BF16) {
                       const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
                       o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
@@ -576,7 +590,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!done) {
 #pragma unroll
               for (int c = 0; c < 16; ++c)
-                if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, tc_finish<G::kIntAcc>(prm, alpha, p, q0 + c0 + c, v[c]));
+                if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c, v[c]));
             }
           }
         } else if (prm.cluster) {
@@ -617,25 +631,41 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int np = min(kBP, prm.P - w.p0);
           const int64_t plane = (int64_t)prm.P * prm.Q;
           const uint32_t* const ws = static_cast<const uint32_t*>(prm.ws);
-          for (int i = et; i < np * nq; i += 128) {
-            const int pl = prm.swap ? i % np : i / nq, ql = prm.swap ? i / np : i % nq;
-            const int pp = w.p0 + pl, qq = q0 + ql;
-            const uint32_t* src = ws + (prm.swap ? (int64_t)qq * prm.P + pp : (int64_t)pp * prm.Q + qq);
-            uint32_t total = 0u;
-            for (int k0 = 0; k0 < ksplit; k0 += 8) {  // 8 loads in flight, added in split order
-              uint32_t part[8];
+          // four output elements per thread at a time, every partial of all four in flight before the first add
+          for (int i0 = et; i0 < np * nq; i0 += 4 * 128) {
+            uint32_t part[4][8];
+            int pp[4], qq[4];
+            const uint32_t* src[4];
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (k0 + j < ksplit) part[j] = __ldcg(src + (int64_t)(k0 + j) * plane);
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (k0 + j < ksplit) {
-                  if (k0 + j == 0) total = part[j];
-                  else if constexpr (G::kIntAcc) total = (uint32_t)((int32_t)total + (int32_t)part[j]);
-                  else total = __float_as_uint(__uint_as_float(total) + __uint_as_float(part[j]));
-                }
+            for (int e = 0; e < 4; ++e) {
+              const int i = i0 + e * 128;
+              const int ii = i < np * nq ? i : 0;
+              const int pl = prm.swap ? ii % np : ii / nq, ql = prm.swap ? ii / np : ii % nq;
+              pp[e] = w.p0 + pl;
+              qq[e] = q0 + ql;
+              src[e] = ws + (prm.swap ? (int64_t)qq[e] * prm.P + pp[e] : (int64_t)pp[e] * prm.Q + qq[e]);
             }
-            tc_store(prm, pp, qq, tc_finish<G::kIntAcc>(prm, alpha, pp, qq, total));
+            uint32_t total[4] = {0u, 0u, 0u, 0u};
+            for (int k0 = 0; k0 < ksplit; k0 += 8) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (k0 + j < ksplit) part[e][j] = __ldcg(src[e] + (int64_t)(k0 + j) * plane);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (k0 + j < ksplit) {  // added in split order
+                    if (k0 + j == 0) total[e] = part[e][j];
+                    else if constexpr (G::kIntAcc) total[e] = (uint32_t)((int32_t)total[e] + (int32_t)part[e][j]);
+                    else total[e] = __float_as_uint(__uint_as_float(total[e]) + __uint_as_float(part[e][j]));
+                  }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (i0 + e * 128 < np * nq)
+                tc_store(prm, pp[e], qq[e], tc_finish<G::kIntAcc>(prm, alpha, pp[e], qq[e], total[e]));
           }
           if (et == 0) prm.counters[w.tile] = 0u;
         }
