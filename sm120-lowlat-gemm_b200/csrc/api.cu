@@ -356,8 +356,23 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
     case LLG_KIND_NVFP4: p.idesc = (1u << 7) | (1u << 10) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;  // e2m1, ue4m3 scales
   }
 
+  // Row pitch of the A tiles. A 128-row MMA tile may own fewer rows: with a whole K range per CTA (no split-K) the
+  // pitch is shrunk until the tiles fill the last round of SMs evenly, e.g. 14336 rows -> 148 tiles of 97 rows instead
+  // of 112 tiles of 128 on 148 SMs. The TMA box is as tall as the pitch; the MMA still spans 128 rows.
+  p.p_rows = 128;
+  if (a->ksplit == 1 && !cluster && a->swap) {
+    const int64_t sms = sm_count() > 0 ? sm_count() : 1;
+    const int64_t tq = (Q + tile.bq - 1) / tile.bq, tp0 = (P + 127) / 128;
+    const int64_t rounds = (tp0 * tq + sms - 1) / sms;
+    const int64_t want_tp = rounds * sms / tq;
+    if (want_tp > tp0) {
+      int64_t rows = (P + want_tp - 1) / want_tp;
+      if (rows < 32) rows = 32;  // keep the TMA boxes reasonably tall
+      if (rows < 128) p.p_rows = (int)rows;
+    }
+  }
   CUtensorMap ta, tb;
-  if (!make_map(&ta, a->a, a->a_row_bytes, P, a->lda_bytes, 128, p.a_is_weight) ||
+  if (!make_map(&ta, a->a, a->a_row_bytes, P, a->lda_bytes, p.p_rows, p.a_is_weight) ||
       !make_map(&tb, a->b, a->b_row_bytes, Q, a->ldb_bytes, tile.bq, !p.a_is_weight))
     return fail(LLG_E_CUDA, "cuTensorMapEncodeTiled failed (operand layout not expressible as a TMA map)");
 

@@ -97,6 +97,7 @@ struct TcDev {
   int P, Q, K;          // K in elements
   int k_atoms;          // ceil(K bytes of the streamed (narrower) operand per row / 128)
   int ksplit, stages;
+  int p_rows;           // rows of A one tile owns (128, or fewer to spread a few tiles over all SMs when ksplit == 1)
   int n_items;          // (tile, K partition) pairs a persistent grid walks; 1 per CTA in cluster mode
   uint32_t idesc;
   // split-K

@@ -174,7 +174,7 @@ struct Item {
 
 template <int BQ, int ATOMS>
 __device__ __forceinline__ Item decode_item(const TcDev& prm, int item) {
-  const int tiles_p = (prm.P + kBP - 1) / kBP, tiles_q = (prm.Q + BQ - 1) / BQ;
+  const int tiles_p = (prm.P + prm.p_rows - 1) / prm.p_rows, tiles_q = (prm.Q + BQ - 1) / BQ;
   const int ntile = tiles_p * tiles_q;
   Item w;
   int tile;
@@ -186,7 +186,7 @@ __device__ __forceinline__ Item decode_item(const TcDev& prm, int item) {
     w.split = item / ntile;
   }
   w.tile = (unsigned)tile;
-  w.p0 = (tile % tiles_p) * kBP;
+  w.p0 = (tile % tiles_p) * prm.p_rows;
   w.q0 = (tile / tiles_p) * BQ;
   const int nk = (prm.k_atoms + ATOMS - 1) / ATOMS;
   w.kt_beg = (int)((int64_t)nk * w.split / prm.ksplit);
@@ -248,6 +248,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ================================ TMA producer ================================
     if (lane == 0) {
       const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+      // an A box holds p_rows rows (<= 128): the rows of the 128-row MMA tile below it keep stale data and produce
+      // accumulator rows nobody reads
+      const uint32_t tx_bytes = (uint32_t)(ATOMS * prm.p_rows * 128) + (uint32_t)G::kBBytes;
       auto load_a = [&](const Item& w, int it, uint32_t g) {
         const uint32_t s = g % S, st = stage0 + s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
 #pragma unroll
@@ -272,7 +275,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // activation tiles of the same stages
           const int npre = w.ntiles < S ? w.ntiles : S;
           for (int i = 0; i < npre; ++i) {
-            mbar_expect_tx(smem_u32(&hdr->full[i]), G::kTxBytes);
+            mbar_expect_tx(smem_u32(&hdr->full[i]), tx_bytes);
             if (a_first) load_a(w, i, (uint32_t)i); else load_b(w, i, (uint32_t)i);
           }
           pdl_wait();
@@ -289,7 +292,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ok = mbar_wait(smem_u32(&hdr->empty[s]), ((g / S) & 1) ^ 1, abort_word);
             if (!ok) { give_up(prm, ST_PRODUCER_EMPTY_WAIT); break; }
           }
-          mbar_expect_tx(smem_u32(&hdr->full[s]), G::kTxBytes);
+          mbar_expect_tx(smem_u32(&hdr->full[s]), tx_bytes);
           load_a(w, it, g);
           load_b(w, it, g);
         }
@@ -523,8 +526,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int nq = min(BQ, prm.Q - w.q0);
       const int q0 = w.q0;
       // row-side epilogue operands are fetched while the MMAs still run
+      const bool row_ok = p < prm.P && r < prm.p_rows;  // rows past the pitch belong to the next tile
       float rs = 1.f, bias_p = 0.f;
-      if (ksplit == 1 && p < prm.P) {
+      if (ksplit == 1 && row_ok) {
         rs = tc_vec(prm.row_scale, prm.row_scale_len, p);
         if (prm.bias_dtype != LLG_DT_NONE && prm.bias_on_p) bias_p = tc_bias(prm, p);
       }
@@ -547,7 +551,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int c = 0; c < 16; ++c) v[c] = 0u;
         }
         if (ksplit == 1) {
-          if (p < prm.P) {
+          if (row_ok) {
             bool done = false;
             if (!prm.swap && c0 + 16 <= nq) {
               // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
@@ -744,7 +748,8 @@ cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
       if (e != cudaSuccess) return e;
       if (dev < 32) attr_done |= 1u << dev;
     }
-    const int64_t tiles = (int64_t)((p.P + kBP - 1) / kBP) * ((p.Q + BQ - 1) / BQ);
+    if (p.cluster || p.ksplit > 1 || p.p_rows < 8 || p.p_rows > kBP) p.p_rows = kBP;  // ragged rows only without split-K
+    const int64_t tiles = (int64_t)((p.P + p.p_rows - 1) / p.p_rows) * ((p.Q + BQ - 1) / BQ);
     dim3 grid;
     if (p.cluster) {
       if (tiles > INT32_MAX) return cudaErrorInvalidValue;

@@ -1,0 +1,112 @@
+"""Tensor-parallel decode step on two CPU ranks (gloo): sharding arithmetic and the all-reduce placement, with a host
+matmul injected where the product uses the CUDA GEMM. No GPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from lowlat_gemm import tp as TP
+
+SHAPE = TP.LayerShape(hidden=64, qkv=96, inter=128)
+LAYERS = 2
+M = 3
+
+
+def host_gemm(x, w, out_dtype=None, **kw):
+    """float64 x @ w^T: exact enough that only the collective's summation order separates TP1 from TP2."""
+    return x.double() @ w.double().T
+
+
+def full_weights():
+    g = torch.Generator().manual_seed(123)
+    out = []
+    for _ in range(LAYERS):
+        out.append({"qkv": torch.randn(SHAPE.qkv, SHAPE.hidden, generator=g) / 8,
+                    "o": torch.randn(SHAPE.hidden, SHAPE.hidden, generator=g) / 8,
+                    "gate_up": torch.randn(2 * SHAPE.inter, SHAPE.hidden, generator=g) / 8,
+                    "down": torch.randn(SHAPE.hidden, SHAPE.inter, generator=g) / 12})
+    return out
+
+
+def build_step(tp, rank, group=None):
+    step = TP.DecodeStep("bf16", LAYERS, tp, rank, "cpu", shape=SHAPE, group=group, gemm_fn=host_gemm)
+    for layer, full in zip(step.layers, full_weights()):
+        layer.w = {"qkv": (TP.shard_rows(full["qkv"], tp, rank), {}), "o": (TP.shard_cols(full["o"], tp, rank), {}),
+                   "gate_up": (TP.shard_gate_up(full["gate_up"], tp, rank), {}),
+                   "down": (TP.shard_cols(full["down"], tp, rank), {})}
+    return step
+
+
+def emulate(tp, x):
+    """The same step without processes: every rank's partial computed in turn, row-parallel outputs summed."""
+    fulls = full_weights()
+    x = x.double()
+    for full in fulls:
+        o = torch.zeros(M, SHAPE.hidden, dtype=torch.float64)
+        for r in range(tp):
+            qkv = x @ TP.shard_rows(full["qkv"], tp, r).double().T
+            o += qkv[:, : SHAPE.hidden // tp] @ TP.shard_cols(full["o"], tp, r).double().T
+        d = torch.zeros(M, SHAPE.hidden, dtype=torch.float64)
+        for r in range(tp):
+            gu = o @ TP.shard_gate_up(full["gate_up"], tp, r).double().T
+            half = gu.shape[1] // 2
+            d += (torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]) @ TP.shard_cols(full["down"], tp, r).double().T
+        x = d
+    return x
+
+
+def _rank_main(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        x = torch.randn(M, SHAPE.hidden, generator=torch.Generator().manual_seed(7))
+        step = build_step(world, rank)
+        y = step.run(x)
+        torch.save({"y": y, "collectives": step.collectives, "gemms": step.gemms}, f"{out}/rank{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_shards_partition_the_full_weights():
+    full = full_weights()[0]
+    for tp in (1, 2, 4):
+        assert torch.equal(torch.cat([TP.shard_rows(full["qkv"], tp, r) for r in range(tp)]), full["qkv"])
+        assert torch.equal(torch.cat([TP.shard_cols(full["down"], tp, r) for r in range(tp)], dim=1), full["down"])
+        halves = [TP.shard_gate_up(full["gate_up"], tp, r) for r in range(tp)]
+        gate = torch.cat([h[: h.shape[0] // 2] for h in halves])
+        up = torch.cat([h[h.shape[0] // 2:] for h in halves])
+        assert torch.equal(torch.cat([gate, up]), full["gate_up"])
+        shapes = SHAPE.shards(tp)
+        assert shapes["qkv"] == (SHAPE.qkv // tp, SHAPE.hidden) and shapes["down"] == (SHAPE.hidden, SHAPE.inter // tp)
+    with pytest.raises(ValueError):
+        SHAPE.shards(5)
+    big = TP.LayerShape().shards(8)
+    assert big == {"qkv": (1280, 8192), "o": (8192, 1024), "gate_up": (7168, 8192), "down": (8192, 3584)}
+
+
+def test_single_rank_step_equals_emulation():
+    x = torch.randn(M, SHAPE.hidden, generator=torch.Generator().manual_seed(7))
+    step = build_step(1, 0)
+    y = step.run(x)
+    assert step.collectives == 0 and step.gemms == 4 * LAYERS
+    assert torch.allclose(y, emulate(1, x), rtol=1e-12, atol=1e-12)
+
+
+def test_two_gloo_ranks_match_emulation(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    x = torch.randn(M, SHAPE.hidden, generator=torch.Generator().manual_seed(7))
+    want = emulate(2, x)
+    got = [torch.load(tmp_path / f"rank{r}.pt") for r in range(2)]
+    for g in got:
+        assert g["collectives"] == 2 * LAYERS and g["gemms"] == 4 * LAYERS
+        assert torch.allclose(g["y"], want, rtol=1e-11, atol=1e-11)
+    assert torch.equal(got[0]["y"], got[1]["y"])  # replicated after the last all-reduce
+    # and TP2 computes the same function as a differently-sharded TP1 up to the head stand-in: only check finiteness there
+    assert np.isfinite(want.numpy()).all()
