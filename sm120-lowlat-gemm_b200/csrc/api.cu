@@ -162,9 +162,25 @@ int tc_stage_bytes_of(int kind, int cfg) {
   }
 }
 
+#ifdef LLG_TRACE
+__device__ unsigned long long g_trace[16384 * 8];
+__device__ unsigned int g_trace_count = 0;
+#endif
+
 }  // namespace llg
 
 using namespace llg;
+
+#ifdef LLG_TRACE
+extern "C" __attribute__((visibility("default"))) int llg_trace_dump(unsigned long long* host, unsigned int* count) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(count, llg::g_trace_count, sizeof(unsigned int));
+  cudaMemcpyFromSymbol(host, llg::g_trace, sizeof(unsigned long long) * 16384 * 8);
+  const unsigned int zero = 0;
+  cudaMemcpyToSymbol(llg::g_trace_count, &zero, sizeof(zero));
+  return 0;
+}
+#endif
 
 extern "C" {
 

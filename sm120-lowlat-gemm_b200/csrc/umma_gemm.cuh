@@ -70,6 +70,7 @@ struct SmemHeader {
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t last;
+  uint32_t trace_slot;
 };
 static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header too large");
 
@@ -167,6 +168,20 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // the loads of the next item and the epilogue of the previous one overlap the MMAs of the current one. With cluster
 // split-K every CTA owns exactly one item (tile = blockIdx.x, partition = rank in the cluster).
 
+#ifdef LLG_TRACE
+// Timeline probes for a diagnostic build only (never compiled into the shipped library).
+extern __device__ unsigned long long g_trace[16384 * 8];
+extern __device__ unsigned int g_trace_count;
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define LLG_STAMP(slot, k) do { if ((slot) < 16384u) g_trace[(slot) * 8 + (k)] = gtime(); } while (0)
+#else
+#define LLG_STAMP(slot, k) do { } while (0)
+#endif
+
 struct Item {
   int p0, q0, split, kt_beg, ntiles;
   unsigned tile;
@@ -212,6 +227,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int item0 = prm.cluster ? 0 : (int)blockIdx.x;
   const int item_step = prm.cluster ? n_items : (int)gridDim.x;  // cluster mode: exactly one pass
 
+#ifdef LLG_TRACE
+  if (tid == 0) {
+    hdr->trace_slot = atomicAdd(&g_trace_count, 1u);
+    LLG_STAMP(hdr->trace_slot, 0);
+    if (hdr->trace_slot < 16384u) g_trace[hdr->trace_slot * 8 + 7] = ((unsigned long long)gridDim.x << 32) | blockIdx.x;
+  }
+#endif
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&hdr->full[s]), 1);
@@ -230,15 +252,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&hdr->tmem_base), G::kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = hdr->tmem_base;
   if (prm.pdl_early) pdl_trigger();
+  uint32_t tmem = 0;
+  if (warp == 0) {
+    // the producer needs only the barriers it has just initialised: it announces them and starts streaming while
+    // the other warps still set up tensor memory
+    __syncwarp();
+    asm volatile("bar.arrive 3, %0;" ::"r"(G::kThreads) : "memory");
+  } else {
+    if (warp == 1) {
+      tmem_alloc(smem_u32(&hdr->tmem_base), G::kTmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 3, %0;" ::"r"(G::kThreads) : "memory");
+    tc_fence_after();
+    tmem = hdr->tmem_base;
+  }
 
   constexpr uint32_t kABufCol = G::kAccBufs * G::kAccCols;  // mixed kinds: widened A buffers
   constexpr uint32_t kSfCol = G::kAccBufs * G::kAccCols;    // nvfp4: block-scale columns
@@ -278,7 +308,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             mbar_expect_tx(smem_u32(&hdr->full[i]), tx_bytes);
             if (a_first) load_a(w, i, (uint32_t)i); else load_b(w, i, (uint32_t)i);
           }
+          LLG_STAMP(hdr->trace_slot, 1);
           pdl_wait();
+          LLG_STAMP(hdr->trace_slot, 2);
           for (int i = 0; i < npre; ++i) {
             if (a_first) load_b(w, i, (uint32_t)i); else load_a(w, i, (uint32_t)i);
           }
@@ -334,6 +366,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if constexpr (G::kMixed) ok = ok && mbar_wait(smem_u32(&hdr->a_full[g & 1]), (g >> 1) & 1, abort_word);
           if (!ok) { give_up(prm, ST_MMA_FULL_WAIT); break; }
           tc_fence_after();
+#ifdef LLG_TRACE
+          if (g == 0) LLG_STAMP(hdr->trace_slot, 3);
+#endif
           if constexpr (G::kMixed) {
             const uint32_t abuf = tmem + kABufCol + (g & 1u) * ATOMS * G::kAColsAtom;
             constexpr int kMmaPerAtom = G::kAColsAtom / 8;  // K = 16 per MMA, 8 columns of widened A
@@ -539,6 +574,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after();
         have_acc = ok;
+#ifdef LLG_TRACE
+        if (et == 0) LLG_STAMP(hdr->trace_slot, 4);
+#endif
       }
       for (int c0 = 0; c0 < BQ; c0 += 16) {
         if (c0 >= nq) break;
@@ -552,6 +590,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (ksplit == 1) {
           if (row_ok) {
+            // column-side factors of the whole chunk first (independent loads in flight together), then the stores
+            float cs[16], cb[16];
+            const bool col_bias = prm.bias_dtype != LLG_DT_NONE && !prm.bias_on_p;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int q = q0 + c0 + c < prm.Q ? q0 + c0 + c : prm.Q - 1;
+              cs[c] = tc_vec(prm.col_scale, prm.col_scale_len, q);
+              cb[c] = col_bias ? tc_bias(prm, q) : 0.f;
+            }
+            float o[16];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const float acc = G::kIntAcc ? (float)(int32_t)v[c] : __uint_as_float(v[c]);
+              float t = __fmul_rn(__fmul_rn(__fmul_rn(acc, alpha), rs), cs[c]);
+              if (prm.bias_dtype != LLG_DT_NONE) t = __fadd_rn(t, prm.bias_on_p ? bias_p : cb[c]);
+              o[c] = t;
+            }
             bool done = false;
             if (!prm.swap && c0 + 16 <= nq) {
               // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
@@ -559,34 +614,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
                 if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-                  for (int c = 0; c < 16; c += 4) {
-                    float4 o;
-                    o.x = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c, v[c]);
-                    o.y = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 1, v[c + 1]);
-                    o.z = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 2, v[c + 2]);
-                    o.w = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 3, v[c + 3]);
-                    *reinterpret_cast<float4*>(dst + c) = o;
-                  }
+                  for (int c = 0; c < 16; c += 4)
+                    *reinterpret_cast<float4*>(dst + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
                   done = true;
                 }
               } else {
                 uint16_t* dst = static_cast<uint16_t*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
                 if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                  uint32_t o[8];
+                  uint32_t w2[8];
 #pragma unroll
                   for (int c = 0; c < 16; c += 2) {
-                    const float a = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c, v[c]);
-                    const float b = tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c + 1, v[c + 1]);
                     if (prm.out_dtype == LLG_DT_BF16) {
-                      const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
-                      o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                      const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(o[c]), __float2bfloat16_rn(o[c + 1]));
+                      w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
                     } else {
-                      const __half2 t = __halves2half2(__float2half_rn(a), __float2half_rn(b));
-                      o[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                      const __half2 t = __halves2half2(__float2half_rn(o[c]), __float2half_rn(o[c + 1]));
+                      w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
                     }
                   }
-                  *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-                  *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                  *reinterpret_cast<uint4*>(dst) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+                  *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w2[4], w2[5], w2[6], w2[7]);
                   done = true;
                 }
               }
@@ -594,7 +641,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!done) {
 #pragma unroll
               for (int c = 0; c < 16; ++c)
-                if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, tc_finish_row<G::kIntAcc>(prm, alpha, rs, bias_p, q0 + c0 + c, v[c]));
+                if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, o[c]);
             }
           }
         } else if (prm.cluster) {
@@ -614,6 +661,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+#ifdef LLG_TRACE
+      if (et == 0) LLG_STAMP(hdr->trace_slot, 6);
+#endif
       if (w.ntiles > 0) {
         // the accumulator buffer may be overwritten by the MMAs of a later item from here on
         tc_fence_before();
@@ -713,6 +763,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+#ifdef LLG_TRACE
+  if (tid == 0) LLG_STAMP(hdr->trace_slot, 5);
+#endif
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, G::kTmemCols);

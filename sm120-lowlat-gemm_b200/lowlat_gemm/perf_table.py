@@ -40,6 +40,7 @@ def main() -> None:
     ap.add_argument("--plans")
     ap.add_argument("--pdl", action="store_true")
     ap.add_argument("--prefetch-next", action="store_true")
+    ap.add_argument("--prefetch-mb", type=float, default=16)
     ap.add_argument("--measured-gbs", type=float, default=6537.6)
     ap.add_argument("--json")
     ap.add_argument("--replays", type=int, default=20)
@@ -62,7 +63,7 @@ def main() -> None:
 
                 def call(w, kw, nxt):
                     if args.prefetch_next:
-                        return L.gemm(x, w, out=out, prefetch=nxt, prefetch_bytes=16 << 20, **kw, **x_kw)
+                        return L.gemm(x, w, out=out, prefetch=nxt, prefetch_bytes=int(args.prefetch_mb * (1 << 20)), **kw, **x_kw)
                     return L.gemm(x, w, out=out, **kw, **x_kw)
 
                 us = timing.time_per_call(call, cold, replays=args.replays)

@@ -52,7 +52,7 @@ def tc_candidates(kind: str, m: int, n: int, k: int, sm_count: int, quick: bool 
 
 
 def tune_shape(kind: str, n: int, k: int, tokens, dev, replays: int = 7, max_calls: int = 0, quick: bool = False,
-               log=print) -> Plan:
+               log=print, prefetch_bytes: int = 0) -> Plan:
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
     cold = timing.ColdWeights(kind, n, k, dev)
     calls = min(max(len(cold), 32), max_calls) if max_calls else max(len(cold), 32)
@@ -65,7 +65,8 @@ def tune_shape(kind: str, n: int, k: int, tokens, dev, replays: int = 7, max_cal
         best = None
         for c in tc_candidates(kind, m, n, k, sm_count, quick):
             try:
-                t = timing.time_per_call(lambda w, kw, nxt: L.gemm(x, w, out=out, plan=Plan(tc={m: c}), **kw, **x_kw),
+                pf = (lambda nxt: {"prefetch": nxt, "prefetch_bytes": prefetch_bytes}) if prefetch_bytes else (lambda nxt: {})
+                t = timing.time_per_call(lambda w, kw, nxt: L.gemm(x, w, out=out, plan=Plan(tc={m: c}), **kw, **x_kw, **pf(nxt)),
                                          cold, calls=calls, replays=replays)
             except RuntimeError:
                 continue
@@ -88,7 +89,8 @@ def tune_shape(kind: str, n: int, k: int, tokens, dev, replays: int = 7, max_cal
                 for tile in SKINNY_TILES:
                     pl = Plan(skinny=SkinnyOrder(lanes_per_row=lanes, ksplit=ks, default_tile=tile, cluster=clu),
                               skinny_max_m=L.SKINNY_MAX_TOKENS)
-                    t = timing.time_per_call(lambda w, kw, nxt: L.gemm(x, w, out=out, plan=pl), cold, calls=calls, replays=replays)
+                    pf = (lambda nxt: {"prefetch": nxt, "prefetch_bytes": prefetch_bytes}) if prefetch_bytes else (lambda nxt: {})
+                    t = timing.time_per_call(lambda w, kw, nxt: L.gemm(x, w, out=out, plan=pl, **pf(nxt)), cold, calls=calls, replays=replays)
                     if bt is None or t < bt[0]:
                         bt = (t, tile)
                 tiles[m] = bt
@@ -121,6 +123,7 @@ def main() -> None:
     ap.add_argument("--max-calls", type=int, default=0, help="cap the calls per timed graph (faster; weights may stay in L2)")
     ap.add_argument("--quick", action="store_true", help="smaller candidate grid")
     ap.add_argument("--pdl", action="store_true")
+    ap.add_argument("--prefetch-next-mb", type=float, default=0, help="every call prefetches this much of the next weight into L2")
     args = ap.parse_args()
 
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -146,7 +149,8 @@ def main() -> None:
                 continue
             toks = [t for t in tokens if t <= s.get("max_m", 1 << 30)]
             print(f"{kind} {s.get('name', '')} {n}x{k}", flush=True)
-            plans[(kind, n, k)] = tune_shape(kind, n, k, toks, dev, args.replays, args.max_calls, args.quick)
+            plans[(kind, n, k)] = tune_shape(kind, n, k, toks, dev, args.replays, args.max_calls, args.quick,
+                                             prefetch_bytes=int(args.prefetch_next_mb * (1 << 20)))
             L.save_plans(args.out, plans, name)
 
 
