@@ -342,23 +342,36 @@ def run_tp(args) -> None:
         with torch.cuda.graph(graph):
             step.run(x)
     gemms_per_step = step.gemms
+    # end to end: the step's activations come from pinned host memory and its result goes back there, every step
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty(TP_M, step.shape.hidden, dtype=torch.bfloat16).pin_memory()
+    with torch.cuda.stream(side):
+        egraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(egraph):
+            x.copy_(x_host, non_blocking=True)
+            y_host.copy_(step.run(x), non_blocking=True)
     for _ in range(max(args.warmup, 3)):
         graph.replay()
+        egraph.replay()
     torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    with ClockSampler(local) as clk:
+
+    def timed(gr) -> float:
+        dist.barrier()
+        torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(args.steps):
-            graph.replay()
+            gr.replay()
         b.record()
         torch.cuda.synchronize()
-        ms = a.elapsed_time(b)
-    dist.barrier()
-    t = torch.tensor([ms], device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+        t = torch.tensor([a.elapsed_time(b)], device=dev)
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with ClockSampler(local) as clk:
+        ms = timed(graph)
+        ms_e2e = timed(egraph)
     total_bytes = step.weight_bytes() * world  # every rank streams its shard; activations are negligible
     if rank == 0:
         value = total_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -370,7 +383,11 @@ def run_tp(args) -> None:
                            "tokens": TP_M, "layers": layers, "parallelism": f"tp{world}", "collective": "nccl all_reduce x2 per layer",
                            "us_per_layer": ms * 1e3 / args.steps / layers, "pdl": L.pdl_enabled(), "launch": "cuda_graph",
                            "cold_weights": f"{layers} layers of distinct weights ({step.weight_bytes() >> 20} MB per rank)"},
-                "e2e": None, "gpu_launches": args.steps * gemms_per_step * 2,
+                "e2e": {"value": total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                        "h2d_bytes_per_step": TP_M * 8192 * 2, "d2h_bytes_per_step": TP_M * 8192 * 2,
+                        "ms_per_step": ms_e2e / args.steps,
+                        "path": "pinned host x -> H2D -> decode layers (quantize_fp8 + gemm + all_reduce) -> D2H pinned y, in a CUDA graph"},
+                "gpu_launches": args.steps * gemms_per_step * 2,
                 "roofline": {"bound": "hbm", "achieved": value / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": value / world / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
                              "note": "per-GPU weight bytes of the step / step time, collectives included"},

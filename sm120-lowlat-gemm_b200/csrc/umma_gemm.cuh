@@ -567,6 +567,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         rs = tc_vec(prm.row_scale, prm.row_scale_len, p);
         if (prm.bias_dtype != LLG_DT_NONE && prm.bias_on_p) bias_p = tc_bias(prm, p);
       }
+      // ... and so are the column-side factors of the first 16 columns (all of them for decode-sized tiles)
+      const bool col_bias = prm.bias_dtype != LLG_DT_NONE && !prm.bias_on_p;
+      float cs0[16], cb0[16];
+      if (ksplit == 1 && row_ok) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int q = q0 + c < prm.Q ? q0 + c : prm.Q - 1;
+          cs0[c] = tc_vec(prm.col_scale, prm.col_scale_len, q);
+          cb0[c] = col_bias ? tc_bias(prm, q) : 0.f;
+        }
+      }
       if (w.ntiles > 0) {
         if (ok) {
           ok = mbar_wait(smem_u32(&hdr->acc_full[ab]), (n_acc / G::kAccBufs) & 1, abort_word);
@@ -592,12 +603,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (row_ok) {
             // column-side factors of the whole chunk first (independent loads in flight together), then the stores
             float cs[16], cb[16];
-            const bool col_bias = prm.bias_dtype != LLG_DT_NONE && !prm.bias_on_p;
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-              const int q = q0 + c0 + c < prm.Q ? q0 + c0 + c : prm.Q - 1;
-              cs[c] = tc_vec(prm.col_scale, prm.col_scale_len, q);
-              cb[c] = col_bias ? tc_bias(prm, q) : 0.f;
+              if (c0 == 0) {  // fetched before the accumulator wait
+                cs[c] = cs0[c];
+                cb[c] = cb0[c];
+              } else {
+                const int q = q0 + c0 + c < prm.Q ? q0 + c0 + c : prm.Q - 1;
+                cs[c] = tc_vec(prm.col_scale, prm.col_scale_len, q);
+                cb[c] = col_bias ? tc_bias(prm, q) : 0.f;
+              }
             }
             float o[16];
 #pragma unroll
