@@ -151,6 +151,21 @@ LLG_API int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* 
  * up a bounded wait; otherwise the code of the first wait that expired. No counterpart in the reference. */
 LLG_API int llg_device_status(uint32_t* status);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * One-shot all-reduce (sum) of a small tensor across the GPUs of one node over peer-mapped ("symmetric") buffers;
+ * the low-latency replacement for an NCCL all_reduce at the row-parallel boundaries of a tensor-parallel decode
+ * layer. buffers_dev / flags_dev are DEVICE arrays of `world` device pointers (index = rank) to every rank's data
+ * buffer and flag words; each rank must have written its partial into buffers_dev[rank] on `stream` (or before)
+ * and must use a different data buffer for consecutive calls (two alternating buffers are enough). The flag words
+ * (ctas * world uint32 per rank) must be zero before the first call and are zero again after every call. Partials
+ * are added in rank order in fp32, so all ranks get identical bits. bytes must be a multiple of 16, buffers 16-byte
+ * aligned, world <= 8, 1 <= ctas <= LLG_AR_MAX_CTAS. Waits are bounded (~1 s): on expiry the device status word
+ * is set (llg_device_status) and the result is undefined, but nothing hangs.
+ * No counterpart in the reference (it has no multi-GPU code). */
+#define LLG_AR_MAX_CTAS 64
+LLG_API int llg_allreduce_oneshot(const void* const* buffers_dev, uint32_t* const* flags_dev, void* out, int64_t bytes,
+                                  int32_t dtype, int32_t rank, int32_t world, int32_t ctas, void* stream);
+
 /* Split-K tensor-core GEMM for callers that must not allocate device memory. Same arguments and result as
  * llg_tc_gemm, except that args->ws / args->counters are ignored: partial sums and arrival counters live in a fixed
  * scratch array inside the library (LLG_STATIC_WS_ELEMS 4-byte partials + LLG_STATIC_COUNTERS counters, about 4 MB,

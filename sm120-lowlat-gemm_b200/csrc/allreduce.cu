@@ -1,0 +1,134 @@
+// One-shot all-reduce (sum) of a small activation tensor across the GPUs of one node, over peer memory.
+//
+// Used at the two row-parallel boundaries of a tensor-parallel decode layer, where the payload is only M x hidden
+// 16-bit values (16 KB per token at hidden 8192): pure latency. Every rank has written its partial into its own
+// symmetric buffer (peer-mapped memory); each rank then reads all partials with plain 16-byte peer loads and adds them
+// in rank order in fp32, so every rank obtains the same bits, run after run. No multicast, no TMA, no NVLS.
+//
+// Synchronisation: each CTA exchanges one flag with the same CTA on every peer (compare-and-swap 0 -> 1 to signal,
+// 1 -> 0 to consume, so flags are back at zero afterwards and the kernel can be replayed from a CUDA graph). Every
+// spin is bounded; on expiry the kernel records a status code and carries on without waiting (the result is then
+// undefined, the device stays usable). Buffers must alternate between consecutive all-reduces (the caller uses two):
+// a rank may still be reading a peer's buffer of all-reduce n while that peer already writes the buffer of n+1.
+//
+// The reference has no collective of any kind; this stands where NCCL's all_reduce would be called.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "llg_internal.h"
+
+namespace llg {
+namespace {
+
+constexpr int kArThreads = 256;
+constexpr long long kArSpinCycles = 2000000000ll;  // ~1 s
+
+__device__ __forceinline__ bool flag_send(uint32_t* slot) {
+  const long long t0 = clock64();
+  while (atomicCAS_system(slot, 0u, 1u) != 0u)
+    if (clock64() - t0 > kArSpinCycles) return false;
+  return true;
+}
+__device__ __forceinline__ bool flag_recv(uint32_t* slot) {
+  const long long t0 = clock64();
+  while (atomicCAS_system(slot, 1u, 0u) != 1u)
+    if (clock64() - t0 > kArSpinCycles) return false;
+  return true;
+}
+
+struct ArDev {
+  const void* const* buffers;   // [world] device pointers, one symmetric buffer per rank (index = rank)
+  uint32_t* const* flags;       // [world] device pointers to each rank's flag words: [ctas][world]
+  void* out;
+  int64_t vecs;                 // 16-byte vectors to reduce
+  int rank, world, dtype;
+  unsigned* status;
+};
+
+template <int DT>
+__device__ __forceinline__ void accumulate(float (&acc)[8], const uint4& v, bool first) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if constexpr (DT == LLG_DT_F32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = first ? __uint_as_float(w[i]) : acc[i] + __uint_as_float(w[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float lo, hi;
+      if constexpr (DT == LLG_DT_BF16) {
+        lo = __uint_as_float(w[i] << 16);
+        hi = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        lo = t.x;
+        hi = t.y;
+      }
+      acc[2 * i] = first ? lo : acc[2 * i] + lo;
+      acc[2 * i + 1] = first ? hi : acc[2 * i + 1] + hi;
+    }
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArDev p) {
+  const int tid = threadIdx.x, cta = blockIdx.x;
+  // ---- all partials of this CTA's peers are written: exchange flags ----
+  __shared__ int failed;
+  if (tid == 0) failed = 0;
+  __syncthreads();
+  if (tid < p.world) {
+    __threadfence_system();
+    bool ok = flag_send(p.flags[tid] + (int64_t)cta * p.world + p.rank);      // tell peer `tid`
+    ok = flag_recv(p.flags[p.rank] + (int64_t)cta * p.world + tid) && ok;     // hear from peer `tid`
+    __threadfence_system();
+    if (!ok) {
+      failed = 1;
+      atomicCAS(p.status, 0u, 16u);
+    }
+  }
+  __syncthreads();
+  // ---- reduce this CTA's share in rank order ----
+  const int64_t per = (p.vecs + gridDim.x - 1) / gridDim.x;
+  const int64_t lo = per * cta, hi = lo + per < p.vecs ? lo + per : p.vecs;
+  for (int64_t i = lo + tid; i < hi; i += kArThreads) {
+    uint4 v[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.world) v[r] = __ldcv(static_cast<const uint4*>(p.buffers[r]) + i);  // volatile: never a stale cached line
+    float acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < p.world) accumulate<DT>(acc, v[r], r == 0);
+    uint4 o;
+    if constexpr (DT == LLG_DT_F32) {
+      o = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+    } else if constexpr (DT == LLG_DT_BF16) {
+      __nv_bfloat162 t[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) t[j] = __halves2bfloat162(__float2bfloat16_rn(acc[2 * j]), __float2bfloat16_rn(acc[2 * j + 1]));
+      o = *reinterpret_cast<const uint4*>(t);
+    } else {
+      __half2 t[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) t[j] = __halves2half2(__float2half_rn(acc[2 * j]), __float2half_rn(acc[2 * j + 1]));
+      o = *reinterpret_cast<const uint4*>(t);
+    }
+    static_cast<uint4*>(p.out)[i] = o;
+  }
+}
+
+}  // namespace
+
+cudaError_t allreduce_launch(const void* const* buffers, uint32_t* const* flags, void* out, int64_t vecs, int rank,
+                             int world, int dtype, int ctas, unsigned* status, cudaStream_t s) {
+  ArDev p{buffers, flags, out, vecs, rank, world, dtype, status};
+  switch (dtype) {
+    case LLG_DT_BF16: allreduce_oneshot_kernel<LLG_DT_BF16><<<ctas, kArThreads, 0, s>>>(p); break;
+    case LLG_DT_F16: allreduce_oneshot_kernel<LLG_DT_F16><<<ctas, kArThreads, 0, s>>>(p); break;
+    case LLG_DT_F32: allreduce_oneshot_kernel<LLG_DT_F32><<<ctas, kArThreads, 0, s>>>(p); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace llg

@@ -411,6 +411,26 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
   return LLG_OK;
 }
 
+int llg_allreduce_oneshot(const void* const* buffers_dev, uint32_t* const* flags_dev, void* out, int64_t bytes,
+                          int32_t dtype, int32_t rank, int32_t world, int32_t ctas, void* stream) {
+  if (!buffers_dev || !flags_dev || !out) return fail(LLG_E_INVALID, "all-reduce: null pointer");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(LLG_E_INVALID, "all-reduce: world must be in [1, 8] and rank inside it, got rank %d of %d", rank, world);
+  if (bytes <= 0 || bytes % 16 || !aligned(out, 16))
+    return fail(LLG_E_INVALID, "all-reduce: size must be a positive multiple of 16 bytes and buffers 16-byte aligned");
+  if (dtype < LLG_DT_BF16 || dtype > LLG_DT_F32) return fail(LLG_E_INVALID, "all-reduce: dtype must be bf16, f16 or f32");
+  if (ctas < 1 || ctas > LLG_AR_MAX_CTAS) return fail(LLG_E_INVALID, "all-reduce: ctas must be in [1, %d]", LLG_AR_MAX_CTAS);
+  unsigned* status = status_word_device_ptr();
+  if (!status) return fail(LLG_E_CUDA, "no device status word");
+  const cudaError_t e = allreduce_launch(buffers_dev, flags_dev, out, bytes / 16, rank, world, dtype, ctas, status,
+                                         static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LLG_E_CUDA, "all-reduce launch failed: %s", cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
 int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream) {
   if (!args) return fail(LLG_E_INVALID, "null arguments");
   // set-up, once per device, with that device current: the device address of the scratch array

@@ -71,6 +71,10 @@ cudaError_t skinny_launch_l8(const SkinnyDev& p, int rows, int unroll, int warps
 cudaError_t skinny_launch_l16(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
 cudaError_t skinny_launch_l32(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
 
+// ---- one-shot all-reduce over peer memory ------------------------------------------------------------------------
+cudaError_t allreduce_launch(const void* const* buffers, uint32_t* const* flags, void* out, int64_t vecs, int rank,
+                             int world, int dtype, int ctas, unsigned* status, cudaStream_t s);
+
 // ---- quantizers --------------------------------------------------------------------------------------------------
 cudaError_t quant_launch(const llg_quant_args& a, cudaStream_t s);
 

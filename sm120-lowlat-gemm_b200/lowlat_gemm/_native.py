@@ -58,6 +58,7 @@ SYMBOLS = {
     "llg_quant": (c_i32, [C.POINTER(QuantArgs), c_ptr]),
     "llg_set_pdl": (None, [c_i32]),
     "llg_pdl_enabled": (c_i32, []),
+    "llg_allreduce_oneshot": (c_i32, [c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_ptr]),
     "llg_tc_gemm_static_ws": (c_i32, [C.POINTER(TcArgs), c_ptr]),
     "llg_tc_gemm_host": (c_i32, [C.POINTER(TcArgs), c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_ptr]),
     "llg_device_status": (c_i32, [C.POINTER(C.c_uint32)]),
