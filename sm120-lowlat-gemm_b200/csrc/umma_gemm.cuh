@@ -35,8 +35,11 @@ struct Geo {
   static constexpr bool kMixed = FAM == FAM_W8A16 || FAM == FAM_W4A16;
   static constexpr bool kNvf4 = FAM == FAM_NVF4;
   static constexpr bool kIntAcc = FAM == FAM_I8;
-  static constexpr bool kHelpers = kMixed || kNvf4;              // warps 6-9: converter / block-scale feeder
-  static constexpr int kThreads = kHelpers ? 320 : 192;
+  static constexpr bool kHelpers = kMixed || kNvf4;              // warps 6..: converter / block-scale feeder
+  // helper threads per tile row: the widening is ALU work, so several warps share each 32-lane quarter of tensor memory
+  static constexpr int kParts = FAM == FAM_W4A16 ? 4 : FAM == FAM_W8A16 ? 2 : 1;
+  static constexpr int kHelperThreads = kHelpers ? 128 * kParts : 0;
+  static constexpr int kThreads = 192 + kHelperThreads;
   static constexpr int kBPerA = FAM == FAM_W8A16 ? 2 : FAM == FAM_W4A16 ? 4 : 1;  // B atoms per A atom
   static constexpr int kBAtomTile = BQ * 128;
   static constexpr int kABytes = ATOMS * kAAtomTile;
@@ -243,7 +246,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&hdr->acc_full[b]), 1);
       mbar_init(smem_u32(&hdr->acc_empty[b]), 128);
-      mbar_init(smem_u32(&hdr->a_full[b]), 128);
+      mbar_init(smem_u32(&hdr->a_full[b]), G::kMixed ? G::kHelperThreads : 128);
       mbar_init(smem_u32(&hdr->a_empty[b]), 1);
     }
     hdr->abort = 0u;
@@ -412,9 +415,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp >= 6) {
     // ================================ helpers: block-scale feeder / weight converter ================================
     if constexpr (G::kHelpers) {
-      const int ht = tid - 192;                // 0..127
+      const int ht = tid - 192;                // 0..kHelperThreads-1
       const int quarter = warp & 3;            // tensor-memory lanes this warp may touch: [32*quarter, +32)
-      const int r = quarter * 32 + lane;       // row of the tile this thread owns
+      const int r = quarter * 32 + lane;       // row of the tile this thread works on
+      const int part = (warp - 6) >> 2;        // which share of the row's 16-byte chunks (mixed kinds)
+      constexpr int kChunks = 8 / G::kParts;   // 16-byte chunks of a 128-byte row per thread
       const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
       bool ok = true;
       uint32_t g = 0;
@@ -446,6 +451,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const int sfk = sfk0 + j * 4;
+                  if (FAM == FAM_W4A16 && (j * G::kParts) / 4 != part) continue;  // another thread of this row owns the piece
                   {
                     const bool v = w.p0 + r < prm.P && sfk < sfk_total;
                     const unsigned char* src = v ? prm.a_sf + (int64_t)(w.p0 + r) * prm.lda_sf + sfk : prm.a_sf;
@@ -484,15 +490,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               const uint32_t abuf = tmem + lane_addr + kABufCol + (gd & 1u) * ATOMS * G::kAColsAtom;
 #pragma unroll
               for (int a = 0; a < ATOMS; ++a) {
-                const uint4 sc = lds128(st + G::kSfAOff + a * 2048 + r * 16);
-                const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                for (int cc = 0; cc < kChunks; ++cc) {
+                  const int c = part * kChunks + cc;
+                  // chunk c holds K [32c, 32c+32) of the atom = scale blocks 2c and 2c+1 = bytes 2c, 2c+1 of the row's 16
+                  uint32_t sc2;
+                  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc2) : "r"(st + G::kSfAOff + a * 2048 + r * 16 + 2 * c));
                   const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
                   const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
-                  // chunk c holds K [32c, 32c+32) of the atom = scale blocks 2c and 2c+1
-                  const uint32_t s0 = widen_scale((scw[c >> 1] >> (16 * (c & 1))) & 0xffu, bf16);
-                  const uint32_t s1 = widen_scale((scw[c >> 1] >> (16 * (c & 1) + 8)) & 0xffu, bf16);
+                  const uint32_t s0 = widen_scale(sc2 & 0xffu, bf16), s1 = widen_scale((sc2 >> 8) & 0xffu, bf16);
 #pragma unroll
                   for (int h = 0; h < 2; ++h) {
                     uint32_t o[8];
@@ -526,7 +532,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int a = 0; a < ATOMS; ++a)
 #pragma unroll
-              for (int c = 0; c < 8; ++c) {
+              for (int cc = 0; cc < kChunks; ++cc) {
+                const int c = part * kChunks + cc;
                 const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
                 uint32_t o[8];
                 widen_e4m3x4(raw.x, bf16, o[0], o[1]);

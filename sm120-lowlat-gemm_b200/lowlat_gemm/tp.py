@@ -81,7 +81,7 @@ class DecodeStep:
     """`layers` decode layers on this rank; run() executes them in order on the current stream."""
 
     def __init__(self, kind: str, layers: int, tp: int, rank: int, device, shape: LayerShape = LayerShape(), group=None,
-                 gemm_fn=None, prefetch_bytes: int = 0, nvfp4_global: float = 64.0):
+                 gemm_fn=None, prefetch_bytes: int = 0, nvfp4_global: float = 64.0, comm=None):
         self.kind, self.tp, self.rank, self.group, self.device = kind, tp, rank, group, device
         self.shape = shape
         self.layers = [DecodeLayer(kind, shape, tp, rank, device, seed=i) for i in range(layers)]
@@ -93,6 +93,8 @@ class DecodeStep:
         self._g4_host = float(nvfp4_global)  # host copy: nothing on the launch path may read the device
         self.collectives = 0
         self.gemms = 0
+        self.comm = comm if tp > 1 else None  # a comm.OneShotAllReduce, or None for NCCL all_reduce
+        self._ar_index = 0
 
     def weight_bytes(self) -> int:
         return sum(l.weight_bytes() for l in self.layers)
@@ -100,11 +102,11 @@ class DecodeStep:
     def _order(self):
         return [(li, name) for li in range(len(self.layers)) for name in ("qkv", "o", "gate_up", "down")]
 
-    def _project(self, h: torch.Tensor, w, kw: dict, nxt) -> torch.Tensor:
+    def _project(self, h: torch.Tensor, w, kw: dict, nxt, out=None) -> torch.Tensor:
         """One projection: activation quantization where the precision needs it, then the GEMM."""
-        extra = {}
+        extra = {} if out is None else {"out": out}
         if nxt is not None and self.prefetch_bytes:
-            extra = {"prefetch": nxt, "prefetch_bytes": min(self.prefetch_bytes, nxt.numel() * nxt.element_size())}
+            extra.update(prefetch=nxt, prefetch_bytes=min(self.prefetch_bytes, nxt.numel() * nxt.element_size()))
         self.gemms += 1
         if self.kind == "fp8":
             q, s = self._q8(h)
@@ -114,13 +116,23 @@ class DecodeStep:
             return self._gemm(q, w, x_block_scale=sf, x_scale=1.0 / self._g4_host, out_dtype=self.act_dtype, **kw, **extra)
         return self._gemm(h, w, out_dtype=self.act_dtype, **kw, **extra)
 
-    def _all_reduce(self, y: torch.Tensor) -> None:
-        if self.tp > 1:
+    def _row_parallel(self, h: torch.Tensor, w, kw: dict, nxt) -> torch.Tensor:
+        """Row-parallel projection followed by the sum over ranks."""
+        if self.tp == 1:
+            return self._project(h, w, kw, nxt)
+        self.collectives += 1
+        if self.comm is None:
+            y = self._project(h, w, kw, nxt)
             dist.all_reduce(y, group=self.group)
-            self.collectives += 1
+            return y
+        idx = self._ar_index
+        self._ar_index += 1
+        part = self._project(h, w, kw, nxt, out=self.comm.view(idx, (h.shape[0], w.shape[0]), self.act_dtype))
+        return self.comm.reduce(idx, torch.empty_like(part))
 
     def run(self, x: torch.Tensor) -> torch.Tensor:
         """x [M, hidden] replicated on every rank -> [M, hidden] replicated (after the last all-reduce)."""
+        self._ar_index = 0
         order = self._order()
         nxt_w = {order[i]: self.layers[order[(i + 1) % len(order)][0]].w[order[(i + 1) % len(order)][1]][0]
                  for i in range(len(order))}
@@ -131,12 +143,9 @@ class DecodeStep:
             attn = qkv[:, :a_width]  # stand-in for this rank's attention heads' output
             if attn.data_ptr() % 16 or (attn.stride(0) * attn.element_size()) % 16:
                 attn = attn.contiguous()  # the GEMM takes strided rows as long as they stay 16-byte aligned
-            o = self._project(attn, *layer.w["o"], nxt_w[(li, "o")])
-            self._all_reduce(o)
+            o = self._row_parallel(attn, *layer.w["o"], nxt_w[(li, "o")])
             gu = self._project(o, *layer.w["gate_up"], nxt_w[(li, "gate_up")])
             half = gu.shape[1] // 2
             act = torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]
-            d = self._project(act, *layer.w["down"], nxt_w[(li, "down")])
-            self._all_reduce(d)
-            x = d
+            x = self._row_parallel(act, *layer.w["down"], nxt_w[(li, "down")])
         return x

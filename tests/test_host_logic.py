@@ -35,7 +35,8 @@ def test_tc_info_table():
     for kind in L.KINDS:
         for cfg in range(L.NUM_CFGS):
             bp, bq, threads, stage = L.tc_info(kind, cfg)
-            assert bp == 128 and bq == 16 << (cfg % 5) and threads == (320 if kind in L._MIXED or kind == "nvfp4" else 192)
+            want = 704 if kind.startswith("w4a16") else 448 if kind.startswith("w8a16") else 320 if kind == "nvfp4" else 192
+            assert bp == 128 and bq == 16 << (cfg % 5) and threads == want
             assert stage % 1024 == 0 and (stage == 0) == (L.max_stages(kind, cfg) == 0)
     assert L.tc_info("bf16", 0)[3] == 128 * 128 + 16 * 128
     assert L.tc_info("nvfp4", 4)[3] == 0 and L.tc_info("w4a16_bf16", 5)[3] == 0
