@@ -318,6 +318,12 @@ def run_single(args) -> None:
 # N > 1: config 5, tensor-parallel decode step
 
 
+def _progress(msg: str) -> None:
+    """Progress marker for multi-rank runs (rank 0 only), flushed at once so a stalled run shows where it stopped."""
+    if os.environ.get("RANK", "0") == "0":
+        print(f"[bench {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_tp(args) -> None:
     import torch.distributed as dist
     import lowlat_gemm as L
@@ -326,9 +332,15 @@ def run_tp(args) -> None:
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
+    _progress("process group up")
     L.set_pdl(not args.no_pdl)
     layers = args.layers
-    step = TP.DecodeStep(TP_KIND, layers, world, rank, dev, prefetch_bytes=0)
+    comm = None
+    if args.allreduce == "oneshot":
+        from lowlat_gemm import comm as CM
+        comm = CM.OneShotAllReduce(None, dev, max_bytes=TP_M * 8192 * 2, ctas=16)
+    step = TP.DecodeStep(TP_KIND, layers, world, rank, dev, prefetch_bytes=0, comm=comm)
+    _progress("weights built")
     x = torch.randn(TP_M, step.shape.hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).to(torch.bfloat16) * 0.05
     elems = cnts = 0
     for n, k in step.shape.shards(world).values():
@@ -342,12 +354,14 @@ def run_tp(args) -> None:
             step.run(x)
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
+    _progress("eager warm-up done")
     step.gemms = step.collectives = 0
     with torch.cuda.stream(side):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             step.run(x)
     gemms_per_step = step.gemms
+    _progress("step captured")
     # end to end: the step's activations come from pinned host memory and its result goes back there, every step
     x_host = x.cpu().pin_memory()
     y_host = torch.empty(TP_M, step.shape.hidden, dtype=torch.bfloat16).pin_memory()
@@ -356,10 +370,12 @@ def run_tp(args) -> None:
         with torch.cuda.graph(egraph):
             x.copy_(x_host, non_blocking=True)
             y_host.copy_(step.run(x), non_blocking=True)
+    _progress("e2e step captured")
     for _ in range(max(args.warmup, 3)):
         graph.replay()
         egraph.replay()
     torch.cuda.synchronize()
+    _progress("graph warm-up done")
 
     def timed(gr) -> float:
         dist.barrier()
@@ -386,7 +402,8 @@ def run_tp(args) -> None:
                 "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
                 "config": {"workload": "c5_tp_decode_step", "hidden": 8192, "qkv": 10240, "gate_up": 57344, "down": 28672,
-                           "tokens": TP_M, "layers": layers, "parallelism": f"tp{world}", "collective": "nccl all_reduce x2 per layer",
+                           "tokens": TP_M, "layers": layers, "parallelism": f"tp{world}",
+                           "collective": ("one-shot peer-memory all-reduce" if comm is not None else "nccl all_reduce") + " x2 per layer",
                            "us_per_layer": ms * 1e3 / args.steps / layers, "pdl": L.pdl_enabled(), "launch": "cuda_graph",
                            "cold_weights": f"{layers} layers of distinct weights ({step.weight_bytes() >> 20} MB per rank)"},
                 "e2e": {"value": total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
@@ -399,7 +416,14 @@ def run_tp(args) -> None:
                              "note": "per-GPU weight bytes of the step / step time, collectives included"},
                 "cpu_baseline": None, "clocks": clk.summary()}
         print(json.dumps(line), flush=True)
+    # CUDA graphs that hold NCCL kernels must go before the communicator does, or teardown can block; a watchdog ends
+    # the process in any case once the result is out
+    threading.Timer(30.0, lambda: os._exit(0)).start()
+    del graph, egraph
+    torch.cuda.synchronize()
+    dist.barrier()
     dist.destroy_process_group()
+    os._exit(0)
 
 
 def main() -> None:
@@ -410,6 +434,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--allreduce", choices=("nccl", "oneshot"), default="nccl")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
