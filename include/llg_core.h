@@ -135,6 +135,21 @@ typedef struct llg_quant_args {
 
 LLG_API int llg_quant(const llg_quant_args* args, void* stream);
 
+/* Gated activation fused with the quantizer: per row act = round_to_input_type(silu(gate) * up) (fp32 arithmetic, one
+ * rounding - the tensor a separate SiLU-and-multiply kernel would have stored), then the quantizer of q.mode on act
+ * (LLG_QUANT_FP8_PER_TOKEN, LLG_QUANT_NVFP4) or no quantizer at all (LLG_QUANT_NONE: only `act` is written). q.x is the
+ * gate, `up` the other half; `act` (optional unless mode is NONE) receives the activation in the input type. The step
+ * on the input side of the down projection (reference: the "act" stand-ins of tools/decode_step.py:27-40, which it
+ * leaves to the framework); it removes two elementwise launches per decode layer. */
+#define LLG_QUANT_NONE 4
+typedef struct llg_gated_quant_args {
+  llg_quant_args q;
+  const void* up; int64_t ldup;     /* [M,K], row stride in elements */
+  void* act; int64_t ldact;         /* [M,K] in the input type, or NULL */
+} llg_gated_quant_args;
+
+LLG_API int llg_gated_quant(const llg_gated_quant_args* args, void* stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Process-wide programmatic-dependent-launch switch; stands in for torch.ops.lowlat_gemm.set_pdl / pdl_enabled
  * (reference csrc/ops.cpp:409-410, csrc/tc_info.cu:67-70). */

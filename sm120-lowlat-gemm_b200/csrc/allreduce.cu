@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 
 #include "llg_internal.h"
+#include "ptx_sm100.cuh"
 
 namespace llg {
 namespace {
@@ -72,6 +73,8 @@ __device__ __forceinline__ void accumulate(float (&acc)[8], const uint4& v, bool
 template <int DT>
 __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArDev p) {
   const int tid = threadIdx.x, cta = blockIdx.x;
+  pdl_trigger();  // the GEMM behind this kernel may start streaming its weight
+  pdl_wait();     // the GEMM before it must have finished writing this rank's partial
   // ---- all partials of this CTA's peers are written: exchange flags ----
   __shared__ int failed;
   if (tid == 0) failed = 0;
@@ -122,13 +125,14 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArD
 cudaError_t allreduce_launch(const void* const* buffers, uint32_t* const* flags, void* out, int64_t vecs, int rank,
                              int world, int dtype, int ctas, unsigned* status, cudaStream_t s) {
   ArDev p{buffers, flags, out, vecs, rank, world, dtype, status};
+  const bool pdl = pdl_on();
+  const dim3 grid(ctas), block(kArThreads), one(1, 1, 1);
   switch (dtype) {
-    case LLG_DT_BF16: allreduce_oneshot_kernel<LLG_DT_BF16><<<ctas, kArThreads, 0, s>>>(p); break;
-    case LLG_DT_F16: allreduce_oneshot_kernel<LLG_DT_F16><<<ctas, kArThreads, 0, s>>>(p); break;
-    case LLG_DT_F32: allreduce_oneshot_kernel<LLG_DT_F32><<<ctas, kArThreads, 0, s>>>(p); break;
+    case LLG_DT_BF16: return launch_ex(allreduce_oneshot_kernel<LLG_DT_BF16>, grid, block, 0, s, pdl, one, p);
+    case LLG_DT_F16: return launch_ex(allreduce_oneshot_kernel<LLG_DT_F16>, grid, block, 0, s, pdl, one, p);
+    case LLG_DT_F32: return launch_ex(allreduce_oneshot_kernel<LLG_DT_F32>, grid, block, 0, s, pdl, one, p);
     default: return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
 }
 
 }  // namespace llg

@@ -510,10 +510,33 @@ int llg_quant(const llg_quant_args* a, void* stream) {
       break;
   }
   if (!a->x || !a->q) return fail(LLG_E_INVALID, "quant: q must be a 2-D 1-byte tensor with M rows");
-  const cudaError_t e = quant_launch(*a, static_cast<cudaStream_t>(stream));
+  const cudaError_t e = quant_launch(*a, GatedExtra{nullptr, 0, nullptr, 0}, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(LLG_E_CUDA, "quant: launch failed (%s)", cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
+int llg_gated_quant(const llg_gated_quant_args* g, void* stream) {
+  if (!g) return fail(LLG_E_INVALID, "null arguments");
+  const llg_quant_args* a = &g->q;
+  if (a->in_dtype < LLG_DT_BF16 || a->in_dtype > LLG_DT_F32) return fail(LLG_E_INVALID, "quant: x must be bf16, f16 or f32");
+  if (a->mode != LLG_QUANT_FP8_PER_TOKEN && a->mode != LLG_QUANT_NVFP4 && a->mode != LLG_QUANT_NONE)
+    return fail(LLG_E_INVALID, "gated quant: mode must be fp8 per token, nvfp4 or none, got %d", a->mode);
+  if (a->M < 0 || a->K < 0) return fail(LLG_E_INVALID, "quant: x must be a 2-D CUDA tensor with unit last stride");
+  if (a->mode == LLG_QUANT_NVFP4 && a->K % 16) return fail(LLG_E_INVALID, "quant: nvfp4 needs K %% 16 == 0");
+  if (a->M == 0 || a->K == 0) return LLG_OK;
+  if (!a->x || !g->up) return fail(LLG_E_INVALID, "gated quant: gate and up must be device pointers");
+  if (a->mode == LLG_QUANT_NONE && !g->act) return fail(LLG_E_INVALID, "gated quant: mode none needs the activation output");
+  if (a->mode != LLG_QUANT_NONE && !a->q) return fail(LLG_E_INVALID, "quant: q must be a 2-D 1-byte tensor with M rows");
+  if (a->mode == LLG_QUANT_FP8_PER_TOKEN && !a->scale_out) return fail(LLG_E_INVALID, "quant: per-token modes need scale_out float32[M]");
+  if (a->mode == LLG_QUANT_NVFP4 && (!a->sf_out || !a->scale_in || a->ldq % 8 || !aligned(a->q, 8)))
+    return fail(LLG_E_INVALID, "quant: nvfp4 needs sf [M, K/16] bytes, scale_in float32[1] and 8-byte aligned q rows");
+  const cudaError_t e = quant_launch(*a, GatedExtra{g->up, g->ldup, g->act, g->ldact}, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LLG_E_CUDA, "gated quant: launch failed (%s)", cudaGetErrorString(e));
   }
   return LLG_OK;
 }

@@ -76,7 +76,13 @@ cudaError_t allreduce_launch(const void* const* buffers, uint32_t* const* flags,
                              int world, int dtype, int ctas, unsigned* status, cudaStream_t s);
 
 // ---- quantizers --------------------------------------------------------------------------------------------------
-cudaError_t quant_launch(const llg_quant_args& a, cudaStream_t s);
+struct GatedExtra {
+  const void* up;  // non-null: the input row is silu(x) * up
+  int64_t ldup;
+  void* act;       // optional copy of the activation in the input type
+  int64_t ldact;
+};
+cudaError_t quant_launch(const llg_quant_args& a, const GatedExtra& g, cudaStream_t s);
 
 // ---- tensor-core GEMM --------------------------------------------------------------------------------------------
 // Kernel families (one template instantiation set each).

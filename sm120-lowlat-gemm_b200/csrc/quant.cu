@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "llg_internal.h"
 #include "ptx_sm100.cuh"
 
@@ -70,21 +72,96 @@ __device__ __forceinline__ uint32_t to_s8(float v, float inv) {
 
 struct QuantDev {
   const void* x;
+  const void* up;   // gated input: the row is silu(x) * up, rounded to the input type, before it is quantised
+  void* act;        // optional copy of that row in the input type (mode NONE writes only this)
   void* q;
   void* sf;
   const float* scale_in;
   float* scale_out;
-  int64_t ldx, ldq, ldsf;
+  int64_t ldx, ldup, ldact, ldq, ldsf;
   float min_scale;
   int K;
 };
 
+constexpr int kModeNone = 4;  // gated activation only, no quantisation
+
+template <typename T>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <>
+__device__ __forceinline__ float round_to<float>(float v) { return v; }
+
+// silu(g) * u in fp32, rounded once to the activation type: the value a separate activation kernel would have stored
+template <typename T>
+__device__ __forceinline__ float gated(float g, float u) {
+  return round_to<T>(__fdiv_rn(g, 1.f + expf(-g)) * u);
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  } else {
+    T e[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) e[i] = __float2half_rn(f[i]);
+      else e[i] = __float2bfloat16_rn(f[i]);
+    }
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(e);
+  }
+}
+
 // MODE: LLG_QUANT_*. VEC: rows are 16-byte aligned with K % 8 == 0 and the q rows 8-byte aligned, and the row fits the
 // register budget -> single pass with vector access. Otherwise a scalar two-pass walk that accepts anything.
-template <typename T, int MODE, bool VEC>
+template <typename T, int MODE, bool VEC, bool GATED>
 __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) {
   const int m = blockIdx.x;
+  // let the kernel behind this one (normally the GEMM that consumes q) start streaming its weight right away, then
+  // wait for the producer of x
+  pdl_trigger();
+  pdl_wait();
   const T* x = static_cast<const T*>(p.x) + (int64_t)m * p.ldx;
+  const T* up = GATED ? static_cast<const T*>(p.up) + (int64_t)m * p.ldup : nullptr;
+  T* act = (GATED && p.act) ? static_cast<T*>(p.act) + (int64_t)m * p.ldact : nullptr;
+  // one unit of 8 input values (vector path) / one value (scalar path), gated when asked
+  auto fetch8 = [&](int e0, float (&f)[8]) {
+    load8(x + e0, f);
+    if constexpr (GATED) {
+      float u[8];
+      load8(up + e0, u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = gated<T>(f[i], u[i]);
+      if (act) store8(act + e0, f);
+    }
+  };
+  auto fetch1 = [&](int e) -> float {
+    float v = as_f32(x[e]);
+    if constexpr (GATED) {
+      v = gated<T>(v, as_f32(up[e]));
+      if (act) {
+        if constexpr (sizeof(T) == 4) act[e] = v;
+        else if constexpr (std::is_same<T, __half>::value) act[e] = __float2half_rn(v);
+        else act[e] = __float2bfloat16_rn(v);
+      }
+    }
+    return v;
+  };
+  if constexpr (MODE == kModeNone) {
+    if constexpr (VEC) {
+      for (int u8 = threadIdx.x; u8 < (p.K >> 3); u8 += kThreads) {
+        float f[8];
+        fetch8(u8 * 8, f);
+      }
+    } else {
+      for (int k = threadIdx.x; k < p.K; k += kThreads) fetch1(k);
+    }
+    return;
+  }
   uint8_t* q = static_cast<uint8_t*>(p.q) + (int64_t)m * p.ldq;
   const int tid = threadIdx.x;
 
@@ -96,13 +173,13 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
       float v[16];
       if constexpr (VEC) {
         float lo[8], hi[8];
-        load8(x + b * 16, lo);
-        load8(x + b * 16 + 8, hi);
+        fetch8(b * 16, lo);
+        fetch8(b * 16 + 8, hi);
 #pragma unroll
         for (int e = 0; e < 8; ++e) { v[e] = lo[e]; v[8 + e] = hi[e]; }
       } else {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) v[e] = as_f32(x[b * 16 + e]);
+        for (int e = 0; e < 16; ++e) v[e] = fetch1(b * 16 + e);
       }
       float a = 0.f;
 #pragma unroll
@@ -132,7 +209,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
       for (int j = 0; j < kUnitsCap; ++j) {
         const int u = tid + j * kThreads;
         if (u < units) {
-          load8(x + u * 8, r[j]);
+          fetch8(u * 8, r[j]);
           if constexpr (kPerToken) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) a = fmaxf(a, fabsf(r[j][e]));
@@ -169,7 +246,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
       float scale;
       if constexpr (kPerToken) {
         float a = 0.f;
-        for (int k = tid; k < p.K; k += kThreads) a = fmaxf(a, fabsf(as_f32(x[k])));
+        for (int k = tid; k < p.K; k += kThreads) a = fmaxf(a, fabsf(fetch1(k)));
         a = cta_max(a);
         scale = fmaxf(__fdiv_rn(a, kTop), p.min_scale);
         if (tid == 0) p.scale_out[m] = scale;
@@ -178,8 +255,9 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
       }
       const float inv = __fdiv_rn(1.f, scale);
       for (int k = tid; k < p.K; k += kThreads) {
-        if constexpr (kInt8) q[k] = (uint8_t)to_s8(as_f32(x[k]), inv);
-        else q[k] = (uint8_t)(cvt_e4m3x2(__fmul_rn(as_f32(x[k]), inv), 0.f) & 0xffu);
+        const float xv = fetch1(k);
+        if constexpr (kInt8) q[k] = (uint8_t)to_s8(xv, inv);
+        else q[k] = (uint8_t)(cvt_e4m3x2(__fmul_rn(xv, inv), 0.f) & 0xffu);
       }
     }
   }
@@ -189,38 +267,51 @@ inline bool mult(int64_t v, int64_t n) { return v % n == 0; }
 inline bool ptr_aligned(const void* p, uintptr_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
 
 template <typename T, int MODE>
-cudaError_t launch_mode(const llg_quant_args& a, cudaStream_t s) {
+cudaError_t launch_mode(const llg_quant_args& a, const GatedExtra& g, cudaStream_t s) {
   QuantDev p{};
   p.x = a.x; p.q = a.q; p.sf = a.sf_out; p.scale_in = a.scale_in; p.scale_out = a.scale_out;
   p.ldx = a.ldx; p.ldq = a.ldq; p.ldsf = a.ldsf; p.min_scale = a.min_scale; p.K = a.K;
+  p.up = g.up; p.ldup = g.ldup; p.act = g.act; p.ldact = g.ldact;
   const int64_t in_align = sizeof(T) == 4 ? 32 : 16;
-  bool vec = ptr_aligned(a.x, in_align) && mult(a.ldx * (int64_t)sizeof(T), in_align) && mult(a.K, 8) &&
-             ptr_aligned(a.q, 8) && mult(a.ldq, 8);
-  if (MODE != LLG_QUANT_NVFP4) vec = vec && a.K <= kUnitsCap * 8 * kThreads;
+  const int64_t esz = sizeof(T);
+  bool vec = ptr_aligned(a.x, in_align) && mult(a.ldx * esz, in_align) && mult(a.K, 8);
+  if (MODE != kModeNone) vec = vec && ptr_aligned(a.q, 8) && mult(a.ldq, 8);
+  if (g.up) vec = vec && ptr_aligned(g.up, in_align) && mult(g.ldup * esz, in_align);
+  if (g.act) vec = vec && ptr_aligned(g.act, in_align) && mult(g.ldact * esz, in_align);
+  if (MODE != LLG_QUANT_NVFP4 && MODE != kModeNone) vec = vec && a.K <= kUnitsCap * 8 * kThreads;
   const dim3 grid(a.M), block(kThreads);
-  if (vec) quant_rows_kernel<T, MODE, true><<<grid, block, 0, s>>>(p);
-  else quant_rows_kernel<T, MODE, false><<<grid, block, 0, s>>>(p);
-  return cudaGetLastError();
+  const bool pdl = pdl_on();
+  if (g.up) {
+    if (vec) return launch_ex(quant_rows_kernel<T, MODE, true, true>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
+    return launch_ex(quant_rows_kernel<T, MODE, false, true>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
+  }
+  if constexpr (MODE == kModeNone) {
+    return cudaErrorInvalidValue;
+  } else {
+    if (vec) return launch_ex(quant_rows_kernel<T, MODE, true, false>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
+    return launch_ex(quant_rows_kernel<T, MODE, false, false>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
+  }
 }
 
 template <typename T>
-cudaError_t launch_type(const llg_quant_args& a, cudaStream_t s) {
+cudaError_t launch_type(const llg_quant_args& a, const GatedExtra& g, cudaStream_t s) {
   switch (a.mode) {
-    case LLG_QUANT_FP8_STATIC: return launch_mode<T, LLG_QUANT_FP8_STATIC>(a, s);
-    case LLG_QUANT_FP8_PER_TOKEN: return launch_mode<T, LLG_QUANT_FP8_PER_TOKEN>(a, s);
-    case LLG_QUANT_INT8_PER_TOKEN: return launch_mode<T, LLG_QUANT_INT8_PER_TOKEN>(a, s);
-    case LLG_QUANT_NVFP4: return launch_mode<T, LLG_QUANT_NVFP4>(a, s);
+    case LLG_QUANT_FP8_STATIC: return launch_mode<T, LLG_QUANT_FP8_STATIC>(a, g, s);
+    case LLG_QUANT_FP8_PER_TOKEN: return launch_mode<T, LLG_QUANT_FP8_PER_TOKEN>(a, g, s);
+    case LLG_QUANT_INT8_PER_TOKEN: return launch_mode<T, LLG_QUANT_INT8_PER_TOKEN>(a, g, s);
+    case LLG_QUANT_NVFP4: return launch_mode<T, LLG_QUANT_NVFP4>(a, g, s);
+    case kModeNone: return launch_mode<T, kModeNone>(a, g, s);
     default: return cudaErrorInvalidValue;
   }
 }
 
 }  // namespace
 
-cudaError_t quant_launch(const llg_quant_args& a, cudaStream_t s) {
+cudaError_t quant_launch(const llg_quant_args& a, const GatedExtra& g, cudaStream_t s) {
   switch (a.in_dtype) {
-    case LLG_DT_BF16: return launch_type<__nv_bfloat16>(a, s);
-    case LLG_DT_F16: return launch_type<__half>(a, s);
-    case LLG_DT_F32: return launch_type<float>(a, s);
+    case LLG_DT_BF16: return launch_type<__nv_bfloat16>(a, g, s);
+    case LLG_DT_F16: return launch_type<__half>(a, g, s);
+    case LLG_DT_F32: return launch_type<float>(a, g, s);
     default: return cudaErrorInvalidValue;
   }
 }

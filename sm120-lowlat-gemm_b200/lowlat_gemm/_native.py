@@ -49,6 +49,10 @@ class QuantArgs(C.Structure):
     ]
 
 
+class GatedQuantArgs(C.Structure):
+    _fields_ = [("q", QuantArgs), ("up", c_ptr), ("ldup", c_i64), ("act", c_ptr), ("ldact", c_i64)]
+
+
 # every symbol include/llg_core.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "llg_skinny": (c_i32, [C.POINTER(SkinnyArgs), c_ptr]),
@@ -56,6 +60,7 @@ SYMBOLS = {
     "llg_tc_info": (c_i32, [c_i32, c_i32, C.POINTER(c_i32 * 4)]),
     "llg_smem_budget": (c_i32, []),
     "llg_quant": (c_i32, [C.POINTER(QuantArgs), c_ptr]),
+    "llg_gated_quant": (c_i32, [C.POINTER(GatedQuantArgs), c_ptr]),
     "llg_set_pdl": (None, [c_i32]),
     "llg_pdl_enabled": (c_i32, []),
     "llg_allreduce_oneshot": (c_i32, [c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_ptr]),

@@ -244,3 +244,58 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor):
     sf = torch.empty(rows, k // 16, dtype=torch.uint8, device=x.device)
     torch.ops.lowlat_gemm.quant(x2, q, sf, global_scale.reshape(1).float(), None, 3, 0.0)
     return (q.view(_FP4) if _FP4 is not None else q), sf.view(_FP8)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# gated activation fused with the quantizer (input side of the down projection; no counterpart in the reference)
+
+_DT_CODE = {torch.bfloat16: 1, torch.float16: 2, torch.float32: 3}
+
+
+def _gated(gate_up: torch.Tensor, mode: int, global_scale: torch.Tensor | None, want_act: bool):
+    import ctypes as C
+
+    from . import _native as N
+
+    gu = gate_up.reshape(-1, gate_up.shape[-1])
+    rows, two_k = gu.shape
+    k = two_k // 2
+    if two_k % 2 or gu.stride(1) != 1 or gu.dtype not in _DT_CODE or not gu.is_cuda:
+        raise RuntimeError("lowlat_gemm: gate_up must be a CUDA [M, 2K] bf16/f16/f32 tensor with unit last stride")
+    a = N.GatedQuantArgs()
+    a.q.mode, a.q.in_dtype, a.q.M, a.q.K = mode, _DT_CODE[gu.dtype], rows, k
+    a.q.x, a.q.ldx = gu.data_ptr(), gu.stride(0)
+    a.up, a.ldup = gu.data_ptr() + k * gu.element_size(), gu.stride(0)
+    act = q = s = sf = None
+    if want_act or mode == 4:
+        act = torch.empty(rows, k, dtype=gu.dtype, device=gu.device)
+        a.act, a.ldact = act.data_ptr(), act.stride(0)
+    if mode == 1:
+        q = torch.empty(rows, k, dtype=_FP8, device=gu.device)
+        s = torch.empty(rows, dtype=torch.float32, device=gu.device)
+        a.q.q, a.q.ldq, a.q.scale_out, a.q.min_scale = q.data_ptr(), q.stride(0), s.data_ptr(), 1e-12
+    elif mode == 3:
+        q = torch.empty(rows, k // 2, dtype=torch.uint8, device=gu.device)
+        sf = torch.empty(rows, k // 16, dtype=torch.uint8, device=gu.device)
+        g = global_scale.reshape(1).float()
+        a.q.q, a.q.ldq, a.q.sf_out, a.q.ldsf, a.q.scale_in = q.data_ptr(), q.stride(0), sf.data_ptr(), sf.stride(0), g.data_ptr()
+    with torch.cuda.device(gu.device):
+        N.check(N.lib.llg_gated_quant(C.byref(a), C.c_void_p(torch.cuda.current_stream(gu.device).cuda_stream)))
+    return act, q, s, sf
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[M, 2K] = [gate | up] -> silu(gate) * up as [M, K] in the input type (fp32 arithmetic, one rounding)."""
+    return _gated(gate_up, 4, None, True)[0]
+
+
+def silu_mul_quantize_fp8(gate_up: torch.Tensor):
+    """quantize_fp8(silu_mul(gate_up)) in one kernel: (q float8_e4m3fn [M, K], scale float32 [M])."""
+    _, q, s, _ = _gated(gate_up, 1, None, False)
+    return q, s
+
+
+def silu_mul_quantize_nvfp4(gate_up: torch.Tensor, global_scale: torch.Tensor):
+    """quantize_nvfp4(silu_mul(gate_up), global_scale) in one kernel: (q fp4 [M, K/2], block scales e4m3 [M, K/16])."""
+    _, q, _, sf = _gated(gate_up, 3, global_scale, False)
+    return (q.view(_FP4) if _FP4 is not None else q), sf.view(_FP8)

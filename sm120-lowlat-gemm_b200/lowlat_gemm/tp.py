@@ -74,7 +74,7 @@ class DecodeLayer:
 
 def _default_fns():
     from . import api
-    return api.gemm, api.quantize_fp8, api.quantize_nvfp4
+    return api.gemm, api.quantize_fp8, api.quantize_nvfp4, api
 
 
 class DecodeStep:
@@ -85,8 +85,8 @@ class DecodeStep:
         self.kind, self.tp, self.rank, self.group, self.device = kind, tp, rank, group, device
         self.shape = shape
         self.layers = [DecodeLayer(kind, shape, tp, rank, device, seed=i) for i in range(layers)]
-        g, q8, q4 = _default_fns() if gemm_fn is None else (gemm_fn, None, None)
-        self._gemm, self._q8, self._q4 = g, q8, q4
+        g, q8, q4, api = _default_fns() if gemm_fn is None else (gemm_fn, None, None, None)
+        self._gemm, self._q8, self._q4, self._api = g, q8, q4, api
         self.prefetch_bytes = prefetch_bytes
         self.act_dtype = torch.float16 if kind.endswith("f16") and not kind.endswith("bf16") else torch.bfloat16
         self._g4 = torch.tensor([nvfp4_global], device=device) if kind == "nvfp4" else None
@@ -102,32 +102,38 @@ class DecodeStep:
     def _order(self):
         return [(li, name) for li in range(len(self.layers)) for name in ("qkv", "o", "gate_up", "down")]
 
-    def _project(self, h: torch.Tensor, w, kw: dict, nxt, out=None) -> torch.Tensor:
-        """One projection: activation quantization where the precision needs it, then the GEMM."""
+    def _project(self, h: torch.Tensor, w, kw: dict, nxt, out=None, gated: bool = False) -> torch.Tensor:
+        """One projection: activation quantization where the precision needs it, then the GEMM. With `gated`, h is
+        [gate | up] and the projection's input is silu(gate) * up, fused into the quantizer's kernel."""
         extra = {} if out is None else {"out": out}
         if nxt is not None and self.prefetch_bytes:
             extra.update(prefetch=nxt, prefetch_bytes=min(self.prefetch_bytes, nxt.numel() * nxt.element_size()))
         self.gemms += 1
+        if gated and self._api is None:  # host stand-in used by the CPU tests
+            half = h.shape[1] // 2
+            h, gated = torch.nn.functional.silu(h[:, :half]) * h[:, half:], False
         if self.kind == "fp8":
-            q, s = self._q8(h)
+            q, s = self._api.silu_mul_quantize_fp8(h) if gated else self._q8(h)
             return self._gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
         if self.kind == "nvfp4":
-            q, sf = self._q4(h, self._g4)
+            q, sf = self._api.silu_mul_quantize_nvfp4(h, self._g4) if gated else self._q4(h, self._g4)
             return self._gemm(q, w, x_block_scale=sf, x_scale=1.0 / self._g4_host, out_dtype=self.act_dtype, **kw, **extra)
+        if gated:
+            h = self._api.silu_mul(h)
         return self._gemm(h, w, out_dtype=self.act_dtype, **kw, **extra)
 
-    def _row_parallel(self, h: torch.Tensor, w, kw: dict, nxt) -> torch.Tensor:
+    def _row_parallel(self, h: torch.Tensor, w, kw: dict, nxt, gated: bool = False) -> torch.Tensor:
         """Row-parallel projection followed by the sum over ranks."""
         if self.tp == 1:
-            return self._project(h, w, kw, nxt)
+            return self._project(h, w, kw, nxt, gated=gated)
         self.collectives += 1
         if self.comm is None:
-            y = self._project(h, w, kw, nxt)
+            y = self._project(h, w, kw, nxt, gated=gated)
             dist.all_reduce(y, group=self.group)
             return y
         idx = self._ar_index
         self._ar_index += 1
-        part = self._project(h, w, kw, nxt, out=self.comm.view(idx, (h.shape[0], w.shape[0]), self.act_dtype))
+        part = self._project(h, w, kw, nxt, out=self.comm.view(idx, (h.shape[0], w.shape[0]), self.act_dtype), gated=gated)
         return self.comm.reduce(idx, torch.empty_like(part))
 
     def run(self, x: torch.Tensor) -> torch.Tensor:
@@ -145,7 +151,5 @@ class DecodeStep:
                 attn = attn.contiguous()  # the GEMM takes strided rows as long as they stay 16-byte aligned
             o = self._row_parallel(attn, *layer.w["o"], nxt_w[(li, "o")])
             gu = self._project(o, *layer.w["gate_up"], nxt_w[(li, "gate_up")])
-            half = gu.shape[1] // 2
-            act = torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]
-            x = self._row_parallel(act, *layer.w["down"], nxt_w[(li, "down")])
+            x = self._row_parallel(gu, *layer.w["down"], nxt_w[(li, "down")], gated=True)
         return x

@@ -79,6 +79,27 @@ def test_quantizer_strided_rows_and_empty():
     assert q.shape == (0, 64) and s.shape == (0,)
 
 
+def test_gated_activation_fused_with_quantizers():
+    """silu(gate) * up fused into the quantizer kernel: the activation matches an fp32 torch evaluation to one rounding
+    and the quantized outputs are exactly what the stand-alone quantizers give on that activation."""
+    g = torch.Generator().manual_seed(3)
+    for dt, rows, k in [(torch.bfloat16, 5, 512), (torch.float16, 3, 4096), (torch.bfloat16, 2, 28672 // 2)]:
+        gu = torch.randn(rows, 2 * k, generator=g).to(dt).to(DEV)
+        act = L.silu_mul(gu)
+        ref = (torch.nn.functional.silu(gu[:, :k].float()) * gu[:, k:].float())
+        ulp = ref.abs() * (2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -11) + 1e-30
+        assert act.dtype == dt and bool(((act.float() - ref).abs() <= ulp).all())
+        q, s = L.silu_mul_quantize_fp8(gu)
+        q0, s0 = L.quantize_fp8(act)
+        assert torch.equal(q.view(torch.uint8), q0.view(torch.uint8)) and torch.equal(s, s0)
+        gs = torch.tensor([448 * 6 / act.float().abs().max().item()], device=DEV)
+        q4, sf = L.silu_mul_quantize_nvfp4(gu, gs)
+        q40, sf0 = L.quantize_nvfp4(act, gs)
+        assert torch.equal(q4.view(torch.uint8), q40.view(torch.uint8)) and torch.equal(sf.view(torch.uint8), sf0.view(torch.uint8))
+    view = torch.randn(4, 3 * 256, generator=g).to(torch.bfloat16).to(DEV)[:, :512]  # strided rows
+    assert torch.equal(L.silu_mul(view), L.silu_mul(view.contiguous()))
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # skinny GEMV: bit-exact against the order emulation, M- and tile-invariant
 
