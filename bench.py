@@ -36,6 +36,9 @@ N_OUT, K_IN = 14336, 4096
 TOKENS = (1, 2, 4, 8, 16)
 TP_M = 8
 TP_KIND = "fp8"
+# DRAM bytes one launch of the fp8 GEMM moved in the committed ncu capture (read 58.90 MB + write 0.09 MB, mean of three
+# launches); bench.py cannot run ncu itself
+NCU_DRAM_BYTES_PER_LAUNCH = 58.99e6
 
 
 def peaks() -> dict:
@@ -305,8 +308,9 @@ def run_single(args) -> None:
                 "path": "pinned host x -> H2D -> quantize_fp8 -> gemm -> D2H pinned y (copy-out on a second stream), captured in a CUDA graph"},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                     "kernel": "umma_gemm_kernel<FAM_F8,16,1>", "algorithmic_bytes_per_launch": per_launch_bytes},
+                     "frac": achieved / pk["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": pk["source"],
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, profiles/umma_gemm_fp8_c2_decode.md",
+                     "kernel": "umma_gemm_kernel<FAM_F8,16,2>", "algorithmic_bytes_per_launch": per_launch_bytes},
         "cpu_baseline": {"value": sb / cpu_sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": "median of 3 c2 steps (5 GEMMs each, dequantise + fp32 torch.matmul) on the host"},
         "clocks": clk.summary(), "device_status": status,
