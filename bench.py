@@ -332,15 +332,18 @@ def run_tp(args) -> None:
     import torch.distributed as dist
     import lowlat_gemm as L
     from lowlat_gemm import tp as TP
-    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    multi = world > 1
+    if multi:
+        dist.init_process_group("nccl", device_id=dev)
     _progress("process group up")
     L.set_pdl(not args.no_pdl)
     layers = args.layers
     comm = None
-    if args.allreduce == "oneshot":
+    if args.allreduce == "oneshot" and multi:
         from lowlat_gemm import comm as CM
         comm = CM.OneShotAllReduce(None, dev, max_bytes=TP_M * 8192 * 2, ctas=16)
     step = TP.DecodeStep(TP_KIND, layers, world, rank, dev, prefetch_bytes=0, comm=comm)
@@ -382,7 +385,8 @@ def run_tp(args) -> None:
     _progress("graph warm-up done")
 
     def timed(gr) -> float:
-        dist.barrier()
+        if multi:
+            dist.barrier()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -391,8 +395,9 @@ def run_tp(args) -> None:
         b.record()
         torch.cuda.synchronize()
         t = torch.tensor([a.elapsed_time(b)], device=dev)
-        dist.barrier()
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if multi:
+            dist.barrier()
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
     with ClockSampler(local) as clk:
@@ -422,6 +427,8 @@ def run_tp(args) -> None:
         print(json.dumps(line), flush=True)
     # CUDA graphs that hold NCCL kernels must go before the communicator does, or teardown can block; a watchdog ends
     # the process in any case once the result is out
+    if not multi:
+        return
     threading.Timer(30.0, lambda: os._exit(0)).start()
     del graph, egraph
     torch.cuda.synchronize()
@@ -439,10 +446,12 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--allreduce", choices=("nccl", "oneshot"), default="nccl")
+    ap.add_argument("--workload", choices=("auto", "c2", "c5"), default="auto",
+                    help="auto: config 2 on one GPU, config 5 (tensor-parallel decode step) on several")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    elif int(os.environ.get("WORLD_SIZE", "1")) > 1:
+    elif int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.workload == "c5":
         run_tp(args)
     else:
         run_single(args)
