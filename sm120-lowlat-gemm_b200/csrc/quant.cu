@@ -20,7 +20,9 @@
 namespace llg {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreadsSmall = 256;   // rows up to 16384 elements stay in registers with 256 threads
+constexpr int kThreadsLarge = 1024;  // longer rows (up to 32768): same single pass, four units per thread (64 registers each)
+constexpr int kUnitsLarge = 4;
 constexpr int kUnitsCap = 8;  // 8-element units a thread may keep in registers: rows up to 8 * 8 * 256 = 16384
 
 template <typename T>
@@ -46,6 +48,7 @@ __device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
   }
 }
 
+template <int kThreads>
 __device__ __forceinline__ float cta_max(float v) {
   __shared__ float part[kThreads / 32];
 #pragma unroll
@@ -118,7 +121,7 @@ __device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
 
 // MODE: LLG_QUANT_*. VEC: rows are 16-byte aligned with K % 8 == 0 and the q rows 8-byte aligned, and the row fits the
 // register budget -> single pass with vector access. Otherwise a scalar two-pass walk that accepts anything.
-template <typename T, int MODE, bool VEC, bool GATED>
+template <typename T, int MODE, bool VEC, bool GATED, int kThreads>
 __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) {
   const int m = blockIdx.x;
   // let the kernel behind this one (normally the GEMM that consumes q) start streaming its weight right away, then
@@ -203,10 +206,11 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
     constexpr float kTop = kInt8 ? 127.f : 448.f;
     if constexpr (VEC) {
       const int units = p.K >> 3;
-      float r[kUnitsCap][8];
+      constexpr int kUnits = kThreads == kThreadsLarge ? kUnitsLarge : kUnitsCap;
+      float r[kUnits][8];
       float a = 0.f;
 #pragma unroll
-      for (int j = 0; j < kUnitsCap; ++j) {
+      for (int j = 0; j < kUnits; ++j) {
         const int u = tid + j * kThreads;
         if (u < units) {
           fetch8(u * 8, r[j]);
@@ -218,7 +222,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
       }
       float scale;
       if constexpr (kPerToken) {
-        a = cta_max(a);
+        a = cta_max<kThreads>(a);
         scale = fmaxf(__fdiv_rn(a, kTop), p.min_scale);
         if (tid == 0) p.scale_out[m] = scale;
       } else {
@@ -226,7 +230,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
       }
       const float inv = __fdiv_rn(1.f, scale);
 #pragma unroll
-      for (int j = 0; j < kUnitsCap; ++j) {
+      for (int j = 0; j < kUnits; ++j) {
         const int u = tid + j * kThreads;
         if (u < units) {
           uint32_t w0, w1;
@@ -247,7 +251,7 @@ __global__ void __launch_bounds__(kThreads) quant_rows_kernel(const QuantDev p) 
       if constexpr (kPerToken) {
         float a = 0.f;
         for (int k = tid; k < p.K; k += kThreads) a = fmaxf(a, fabsf(fetch1(k)));
-        a = cta_max(a);
+        a = cta_max<kThreads>(a);
         scale = fmaxf(__fdiv_rn(a, kTop), p.min_scale);
         if (tid == 0) p.scale_out[m] = scale;
       } else {
@@ -278,19 +282,22 @@ cudaError_t launch_mode(const llg_quant_args& a, const GatedExtra& g, cudaStream
   if (MODE != kModeNone) vec = vec && ptr_aligned(a.q, 8) && mult(a.ldq, 8);
   if (g.up) vec = vec && ptr_aligned(g.up, in_align) && mult(g.ldup * esz, in_align);
   if (g.act) vec = vec && ptr_aligned(g.act, in_align) && mult(g.ldact * esz, in_align);
-  if (MODE != LLG_QUANT_NVFP4 && MODE != kModeNone) vec = vec && a.K <= kUnitsCap * 8 * kThreads;
-  const dim3 grid(a.M), block(kThreads);
+  const bool large = a.K > kUnitsCap * 8 * kThreadsSmall;
+  if (MODE != LLG_QUANT_NVFP4 && MODE != kModeNone) vec = vec && a.K <= kUnitsLarge * 8 * kThreadsLarge;
+  const dim3 grid(a.M), one(1, 1, 1);
   const bool pdl = pdl_on();
+#define LLG_QLAUNCH(V, G, TH) launch_ex(quant_rows_kernel<T, MODE, V, G, TH>, grid, dim3(TH), 0, s, pdl, one, p)
   if (g.up) {
-    if (vec) return launch_ex(quant_rows_kernel<T, MODE, true, true>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
-    return launch_ex(quant_rows_kernel<T, MODE, false, true>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
+    if (vec) return large ? LLG_QLAUNCH(true, true, kThreadsLarge) : LLG_QLAUNCH(true, true, kThreadsSmall);
+    return LLG_QLAUNCH(false, true, kThreadsSmall);
   }
   if constexpr (MODE == kModeNone) {
     return cudaErrorInvalidValue;
   } else {
-    if (vec) return launch_ex(quant_rows_kernel<T, MODE, true, false>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
-    return launch_ex(quant_rows_kernel<T, MODE, false, false>, grid, block, 0, s, pdl, dim3(1, 1, 1), p);
+    if (vec) return large ? LLG_QLAUNCH(true, false, kThreadsLarge) : LLG_QLAUNCH(true, false, kThreadsSmall);
+    return LLG_QLAUNCH(false, false, kThreadsSmall);
   }
+#undef LLG_QLAUNCH
 }
 
 template <typename T>

@@ -36,7 +36,7 @@ def no_expired_wait():
 
 
 @pytest.mark.parametrize("shape,dt", [((5, 384), torch.bfloat16), ((3, 4096), torch.bfloat16), ((2, 100), torch.float32),
-                                      ((16, 8192), torch.float16), ((1, 8), torch.bfloat16), ((4, 20000), torch.bfloat16),
+                                      ((16, 8192), torch.float16), ((1, 8), torch.bfloat16), ((4, 20000), torch.bfloat16), ((3, 28672), torch.bfloat16), ((2, 40000), torch.float16),
                                       ((7, 1000), torch.float32)])
 def test_quantizers_bit_exact(shape, dt):
     g = torch.Generator().manual_seed(shape[0] * 7919 + shape[1])
