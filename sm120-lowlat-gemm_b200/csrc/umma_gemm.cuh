@@ -279,7 +279,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ================================ TMA producer ================================
-    if (lane == 0) {
+    // The whole warp walks the loop (addresses, counters and waits stay warp-uniform, so the compiler can keep them in
+    // uniform registers); only the elected lane issues the copies.
+    {
+      const bool leader = elect_one();
       const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
       // an A box holds p_rows rows (<= 128): the rows of the 128-row MMA tile below it keep stale data and produce
       // accumulator rows nobody reads
@@ -307,15 +310,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // the ring is empty: fill it with weight tiles before waiting for the previous kernel, then add the
           // activation tiles of the same stages
           const int npre = w.ntiles < S ? w.ntiles : S;
-          for (int i = 0; i < npre; ++i) {
-            mbar_expect_tx(smem_u32(&hdr->full[i]), tx_bytes);
-            if (a_first) load_a(w, i, (uint32_t)i); else load_b(w, i, (uint32_t)i);
+          if (leader) {
+            for (int i = 0; i < npre; ++i) {
+              mbar_expect_tx(smem_u32(&hdr->full[i]), tx_bytes);
+              if (a_first) load_a(w, i, (uint32_t)i); else load_b(w, i, (uint32_t)i);
+            }
           }
           LLG_STAMP(hdr->trace_slot, 1);
           pdl_wait();
           LLG_STAMP(hdr->trace_slot, 2);
-          for (int i = 0; i < npre; ++i) {
-            if (a_first) load_b(w, i, (uint32_t)i); else load_a(w, i, (uint32_t)i);
+          if (leader) {
+            for (int i = 0; i < npre; ++i) {
+              if (a_first) load_b(w, i, (uint32_t)i); else load_a(w, i, (uint32_t)i);
+            }
           }
           it = npre;
           g = (uint32_t)npre;
@@ -327,9 +334,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ok = mbar_wait(smem_u32(&hdr->empty[s]), ((g / S) & 1) ^ 1, abort_word);
             if (!ok) { give_up(prm, ST_PRODUCER_EMPTY_WAIT); break; }
           }
-          mbar_expect_tx(smem_u32(&hdr->full[s]), tx_bytes);
-          load_a(w, it, g);
-          load_b(w, it, g);
+          if (leader) {
+            mbar_expect_tx(smem_u32(&hdr->full[s]), tx_bytes);
+            load_a(w, it, g);
+            load_b(w, it, g);
+          }
         }
       }
       if (first) pdl_wait();
@@ -349,8 +358,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                       lane, 32);
   } else if (warp == 1) {
     // ================================ MMA issuer ================================
-    if (lane == 0) {
+    // Warp-uniform loop, one elected lane issues (always the same lane, so tcgen05.commit covers its MMAs).
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = prm.idesc;
+      // descriptors of stage 0; a stage or an atom further on only adds to the 14-bit address field (never overflows:
+      // shared memory ends below 256 KB)
+      const uint64_t adesc0 = umma_desc_sw128(stage0 + G::kAOff), bdesc0 = umma_desc_sw128(stage0 + G::kBOff);
+      const uint64_t sfa0 = umma_desc_plain128(stage0 + G::kSfAOff), sfb0 = umma_desc_plain128(stage0 + G::kSfBOff);
       bool ok = true;
       uint32_t g = 0, n_acc = 0;
       for (int item = item0; item < n_items && ok; item += item_step) {
@@ -372,6 +387,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #ifdef LLG_TRACE
           if (g == 0) LLG_STAMP(hdr->trace_slot, 3);
 #endif
+          if (leader) {
           if constexpr (G::kMixed) {
             const uint32_t abuf = tmem + kABufCol + (g & 1u) * ATOMS * G::kAColsAtom;
             constexpr int kMmaPerAtom = G::kAColsAtom / 8;  // K = 16 per MMA, 8 columns of widened A
@@ -379,7 +395,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int a = 0; a < ATOMS; ++a)
 #pragma unroll
               for (int j = 0; j < kMmaPerAtom; ++j) {
-                const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + (a * G::kBPerA + j / 4) * G::kBAtomTile) + (uint64_t)((j % 4) * 2);
+                const uint64_t bdesc = bdesc0 + (uint64_t)((s * G::kStageBytes + (a * G::kBPerA + j / 4) * G::kBAtomTile) >> 4) + (uint64_t)((j % 4) * 2);
                 mma_ts_f16(acc, abuf + a * G::kAColsAtom + j * 8, bdesc, idesc, (it | a | j) != 0);
               }
             umma_commit(smem_u32(&hdr->a_empty[g & 1]));
@@ -387,8 +403,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t sfc = tmem + kSfCol + (g & 1u) * G::kSfColsStage;
 #pragma unroll
             for (int a = 0; a < ATOMS; ++a) {
-              const uint64_t adesc = umma_desc_sw128(st + G::kAOff + a * kAAtomTile);
-              const uint64_t bdesc = umma_desc_sw128(st + G::kBOff + a * G::kBAtomTile);
+              const uint64_t adesc = adesc0 + (uint64_t)((s * G::kStageBytes + a * kAAtomTile) >> 4);
+              const uint64_t bdesc = bdesc0 + (uint64_t)((s * G::kStageBytes + a * G::kBAtomTile) >> 4);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {  // 32 bytes of K per MMA for every kind
                 const uint32_t acc_on = (it | a | j) != 0;
@@ -397,16 +413,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 else if constexpr (FAM == FAM_I8) mma_ss_i8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
                 else {
                   const uint32_t sfa_t = sfc + (uint32_t)(a * 4 + j) * 8, sfb_t = sfa_t + 4;
-                  tmem_cp_32x128b_x4(sfa_t, umma_desc_plain128(st + G::kSfAOff + (a * 4 + j) * 512));
-                  tmem_cp_32x128b_x4(sfb_t, umma_desc_plain128(st + G::kSfBOff + (a * 4 + j) * 512));
+                  const uint64_t sfo = (uint64_t)((s * G::kStageBytes + (a * 4 + j) * 512) >> 4);
+                  tmem_cp_32x128b_x4(sfa_t, sfa0 + sfo);
+                  tmem_cp_32x128b_x4(sfb_t, sfb0 + sfo);
                   mma_ss_nvf4(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on, sfa_t, sfb_t);
                 }
               }
             }
           }
           umma_commit(smem_u32(&hdr->empty[s]));
+          }
         }
-        if (ok) umma_commit(smem_u32(&hdr->acc_full[ab]));
+        if (ok && leader) umma_commit(smem_u32(&hdr->acc_full[ab]));
         ++n_acc;
       }
     }
