@@ -100,6 +100,21 @@ bool make_map(CUtensorMap* m, const void* ptr, int64_t row_bytes, int64_t rows, 
   return r == CUDA_SUCCESS;
 }
 
+// Byte map over a block-scale matrix (one e4m3 byte per 16 K elements): box = 16 bytes x box_rows, no swizzle, so a
+// box lands as [row][16 bytes]. Needs a 16-byte aligned base and row pitch.
+bool make_sf_map(CUtensorMap* m, const void* ptr, int64_t row_bytes, int64_t rows, int64_t ld_bytes, int box_rows) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+  cuuint32_t box[2] = {16u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 bool pdl_on() { return g_pdl.load(std::memory_order_relaxed); }
@@ -392,16 +407,22 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
       !make_map(&tb, a->b, a->b_row_bytes, Q, a->ldb_bytes, tile.bq, !p.a_is_weight))
     return fail(LLG_E_CUDA, "cuTensorMapEncodeTiled failed (operand layout not expressible as a TMA map)");
 
+  CUtensorMap ts = ta;  // only read when sf_tma is set
+  p.sf_tma = 0;
+  if (tc_family_of(a->kind) == FAM_W4A16 && p.a_sf && p.lda_sf % 16 == 0 && aligned(p.a_sf, 16) &&
+      make_sf_map(&ts, p.a_sf, p.K / 16, P, p.lda_sf, p.p_rows))
+    p.sf_tma = 1;
+
   const bool pdl = pdl_on();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   switch (tc_family_of(a->kind)) {
-    case FAM_F16: e = tc_launch_f16(ta, tb, p, a->cfg, pdl, s); break;
-    case FAM_F8: e = tc_launch_f8(ta, tb, p, a->cfg, pdl, s); break;
-    case FAM_I8: e = tc_launch_i8(ta, tb, p, a->cfg, pdl, s); break;
-    case FAM_NVF4: e = tc_launch_nvf4(ta, tb, p, a->cfg, pdl, s); break;
-    case FAM_W8A16: e = tc_launch_w8a16(ta, tb, p, a->cfg, pdl, s); break;
-    default: e = tc_launch_w4a16(ta, tb, p, a->cfg, pdl, s); break;
+    case FAM_F16: e = tc_launch_f16(ta, tb, ts, p, a->cfg, pdl, s); break;
+    case FAM_F8: e = tc_launch_f8(ta, tb, ts, p, a->cfg, pdl, s); break;
+    case FAM_I8: e = tc_launch_i8(ta, tb, ts, p, a->cfg, pdl, s); break;
+    case FAM_NVF4: e = tc_launch_nvf4(ta, tb, ts, p, a->cfg, pdl, s); break;
+    case FAM_W8A16: e = tc_launch_w8a16(ta, tb, ts, p, a->cfg, pdl, s); break;
+    default: e = tc_launch_w4a16(ta, tb, ts, p, a->cfg, pdl, s); break;
   }
   if (e != cudaSuccess) {
     cudaGetLastError();

@@ -119,12 +119,17 @@ __device__ __forceinline__ void tc_store(const TcDev& prm, int p, int q, float v
 // ---- exact widening of 8-bit / 4-bit floats to 16-bit pairs ---------------------------------------------------------
 
 // four e4m3 bytes -> (k0,k1) and (k2,k3) as bf16x2 / f16x2
-__device__ __forceinline__ void widen_e4m3x4(uint32_t w, bool bf16, uint32_t& lo, uint32_t& hi) {
-  if (bf16) {
-    // byte b -> lane (b << 8); sign stays at bit 15, exponent+mantissa move to bits 4..10, which reads as a bf16
-    // 2^-120 too small; the multiply by 2^120 is exact (also for e4m3 subnormals, which become bf16 subnormals)
-    const uint32_t a = __byte_perm(w, 0u, 0x1404), b = __byte_perm(w, 0u, 0x3424);
-    const uint32_t ta = (a & 0x80008000u) | ((a >> 4) & 0x07f007f0u), tb = (b & 0x80008000u) | ((b >> 4) & 0x07f007f0u);
+template <bool BF16>
+__device__ __forceinline__ void widen_e4m3x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  if constexpr (BF16) {
+    // byte s eeee mmm -> bf16 bits with the sign at 15 and exponent+mantissa at 4..10, which reads as the value times
+    // 2^-120; the multiply by 2^120 is exact (also for e4m3 subnormals, which become bf16 subnormals). With the
+    // byte b in the low bits of a 16-bit lane, b * 16 puts everything four bits up and (b & 0x80) * 240 moves the
+    // sign from bit 11 to bit 15; multiplies run on another pipe than the logic operations.
+    uint32_t a, b;
+    asm("prmt.b32 %0, %1, 0, 0x4140;" : "=r"(a) : "r"(w));
+    asm("prmt.b32 %0, %1, 0, 0x4342;" : "=r"(b) : "r"(w));
+    const uint32_t ta = (a & 0x00800080u) * 240u + a * 16u, tb = (b & 0x00800080u) * 240u + b * 16u;
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(ta), "r"(0x7b807b80u));
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(tb), "r"(0x7b807b80u));
   } else {
@@ -132,36 +137,107 @@ __device__ __forceinline__ void widen_e4m3x4(uint32_t w, bool bf16, uint32_t& lo
     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"((uint16_t)(w >> 16)));
   }
 }
-// one e4m3 scale byte -> (s, s) as bf16x2 / f16x2
-__device__ __forceinline__ uint32_t widen_scale(uint32_t s, bool bf16) {
-  uint32_t lo, hi;
-  widen_e4m3x4(s | (s << 8), bf16, lo, hi);
-  return lo;
-}
-// one byte = two e2m1 nibbles (low nibble = even k) -> (k, k+1) as bf16x2 / f16x2, times the block scale pair
-__device__ __forceinline__ uint32_t widen_e2m1x2(uint32_t byte, bool bf16, uint32_t scale2) {
-  uint32_t r;
-  if (bf16) {
-    // nibble s e e m -> bf16 with the three magnitude bits at 6..8: the value times 2^-126 (e = 0 lands in the bf16
-    // subnormals, matching e2m1's 0 / 0.5); the multiply by 2^126 is exact
-    const uint32_t x = (byte & 0x0fu) | ((byte & 0xf0u) << 12);
-    const uint32_t t = ((x & 0x00080008u) << 12) | ((x & 0x00070007u) << 6);
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(t), "r"(0x7e807e80u));
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(r), "r"(scale2));  // <= 6 significant bits: exact
+// Eight e2m1 nibbles of one word (nibble i = K element i) -> four 16-bit pairs (k, k+1), times the block-scale pair.
+//   f16:  the hardware conversion, then one exact multiply (<= 6 significant bits, magnitudes in [2^-10, 2688]).
+//   bf16: nibble s e e m -> bf16 bits with the magnitude at 6..8, which reads as the value times 2^-126 (e = 0 lands
+//         in the bf16 subnormals, matching e2m1's 0 / 0.5). The scale pair arrives multiplied by 2^118, so the one
+//         multiply yields value * scale * 2^-8 exactly (>= 2^-18: never subnormal); the epilogue multiplies the
+//         accumulator by 2^8, which is exact. The bit moves use a multiply (another pipe than the logic operations).
+template <bool BF16>
+__device__ __forceinline__ void widen_e2m1x8(uint32_t w, uint32_t scale2, uint32_t* o) {
+  if constexpr (BF16) {
+    const uint32_t lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // bytes: [even nibble, 0, odd nibble, 0]; a selector with bit 3 set replicates the (clear) top bit of a byte
+      uint32_t x;
+      asm("prmt.b32 %0, %1, %2, %3;" : "=r"(x) : "r"(lo), "r"(hi), "r"((uint32_t)(j | 0x80 | ((4 + j) << 8) | 0x8000)));
+      const uint32_t t = (x * 0x1040u) & 0x81c081c0u;  // magnitude << 6, sign << 12
+      asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(o[j]) : "r"(t), "r"(scale2));
+    }
   } else {
-    asm("{\n\t.reg .b8 b;\n\t.reg .b16 h;\n\tcvt.u16.u32 h, %1;\n\tmov.b16 {b, _}, h;\n\t"
-        "cvt.rn.f16x2.e2m1x2 %0, b;\n\t}\n"
-        : "=r"(r)
-        : "r"(byte));
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(r), "r"(scale2));
+    uint32_t r0, r1, r2, r3;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+        : "r"(w));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(o[0]) : "r"(r0), "r"(scale2));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(o[1]) : "r"(r1), "r"(scale2));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(o[2]) : "r"(r2), "r"(scale2));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(o[3]) : "r"(r3), "r"(scale2));
   }
-  return r;
+}
+// Four e4m3 block-scale bytes -> four replicated 16-bit pairs (s, s); for bf16 each carries the extra 2^118 (see above).
+template <bool BF16>
+__device__ __forceinline__ void widen_scales4(uint32_t sc4, uint32_t* s) {
+  uint32_t p01, p23;
+  widen_e4m3x4<BF16>(sc4, p01, p23);
+  if constexpr (BF16) {
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(p01) : "r"(p01), "r"(0x7a807a80u));  // 2^118: at most 448 * 2^118 < 2^127
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(p23) : "r"(p23), "r"(0x7a807a80u));
+  }
+  s[0] = __byte_perm(p01, 0u, 0x1010);
+  s[1] = __byte_perm(p01, 0u, 0x3232);
+  s[2] = __byte_perm(p23, 0u, 0x1010);
+  s[3] = __byte_perm(p23, 0u, 0x3232);
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+
+// W8A16: one thread's share of a stage: chunks [part * kChunks, +kChunks) of row r of every atom, 16 e4m3 bytes each,
+// widened into 8 columns (2 K per column) of the thread's lane of tensor memory.
+template <class G, int ATOMS, bool BF16>
+__device__ __forceinline__ void w8_widen_stage(uint32_t st, uint32_t abuf, int r, int part) {
+  constexpr int kChunks = 8 / G::kParts;
+#pragma unroll
+  for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+    for (int cc = 0; cc < kChunks; ++cc) {
+      const int c = part * kChunks + cc;
+      const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+      uint32_t o[8];
+      widen_e4m3x4<BF16>(raw.x, o[0], o[1]);
+      widen_e4m3x4<BF16>(raw.y, o[2], o[3]);
+      widen_e4m3x4<BF16>(raw.z, o[4], o[5]);
+      widen_e4m3x4<BF16>(raw.w, o[6], o[7]);
+      tmem_st8(abuf + a * G::kAColsAtom + c * 8, o);
+    }
+}
+
+// W4A16: one thread's share of a stage. Row r of every atom is 128 bytes = 8 chunks of 32 K elements; chunk c holds
+// scale blocks 2c and 2c+1, i.e. bytes 2c and 2c+1 of the row's 16 scale bytes. The thread owns chunks
+// [part * kChunks, +kChunks) and writes them, widened and scaled, to its lane of tensor memory (2 K per column).
+template <class G, int ATOMS, bool BF16>
+__device__ __forceinline__ void w4_widen_stage(uint32_t st, uint32_t abuf, int r, int part) {
+  constexpr int kChunks = 8 / G::kParts;
+  static_assert(kChunks % 2 == 0, "scales are fetched four at a time");
+#pragma unroll
+  for (int a = 0; a < ATOMS; ++a) {
+#pragma unroll
+    for (int cp = 0; cp < kChunks / 2; ++cp) {
+      const int c0 = part * kChunks + 2 * cp;
+      uint32_t sc4, sc[4];
+      asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc4) : "r"(st + G::kSfAOff + a * 2048 + r * 16 + 2 * c0));
+      widen_scales4<BF16>(sc4, sc);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = c0 + cc;
+        const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+        uint32_t o[8];
+        widen_e2m1x8<BF16>(raw.x, sc[cc * 2], o);
+        widen_e2m1x8<BF16>(raw.y, sc[cc * 2], o + 4);
+        tmem_st8(abuf + a * G::kAColsAtom + c * 16, o);
+        widen_e2m1x8<BF16>(raw.z, sc[cc * 2 + 1], o);
+        widen_e2m1x8<BF16>(raw.w, sc[cc * 2 + 1], o + 4);
+        tmem_st8(abuf + a * G::kAColsAtom + c * 16 + 8, o);
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -214,7 +290,8 @@ __device__ __forceinline__ Item decode_item(const TcDev& prm, int item) {
 
 template <int FAM, int BQ, int ATOMS>
 __global__ void __launch_bounds__(Geo<FAM, BQ, ATOMS>::kThreads, 1)
-umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcDev prm) {
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmS, const TcDev prm) {
   using G = Geo<FAM, BQ, ATOMS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_base = smem_u32(smem_raw);
@@ -254,6 +331,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (FAM == FAM_W4A16 && prm.sf_tma) tma_prefetch_desc(&tmS);
   }
   if (prm.pdl_early) pdl_trigger();
   uint32_t tmem = 0;
@@ -286,13 +364,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
       // an A box holds p_rows rows (<= 128): the rows of the 128-row MMA tile below it keep stale data and produce
       // accumulator rows nobody reads
-      const uint32_t tx_bytes = (uint32_t)(ATOMS * prm.p_rows * 128) + (uint32_t)G::kBBytes;
+      // W4A16 with 16-byte aligned scale rows: the 16 block-scale bytes per row and atom travel with the tile
+      const bool sf_tma = FAM == FAM_W4A16 && prm.sf_tma;
+      const uint32_t tx_bytes = (uint32_t)(ATOMS * prm.p_rows * (sf_tma ? 144 : 128)) + (uint32_t)G::kBBytes;
       auto load_a = [&](const Item& w, int it, uint32_t g) {
         const uint32_t s = g % S, st = stage0 + s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
 #pragma unroll
-        for (int a = 0; a < ATOMS; ++a)
+        for (int a = 0; a < ATOMS; ++a) {
           tma_load_2d(st + G::kAOff + a * kAAtomTile, &tmA, bar, ((w.kt_beg + it) * ATOMS + a) * kAtomBytes, w.p0,
                       a_first ? pol_w : pol_x);
+          if constexpr (FAM == FAM_W4A16) {
+            if (sf_tma)
+              tma_load_2d(st + G::kSfAOff + a * 2048, &tmS, bar, ((w.kt_beg + it) * ATOMS + a) * 16, w.p0,
+                          a_first ? pol_w : pol_x);
+          }
+        }
       };
       auto load_b = [&](const Item& w, int it, uint32_t g) {
         const uint32_t s = g % S, st = stage0 + s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
@@ -441,7 +527,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
       bool ok = true;
       uint32_t g = 0;
-      if constexpr (G::kNvf4 || FAM == FAM_W4A16) {
+      if (FAM == FAM_W4A16 && prm.sf_tma) {
+        // ---- W4A16, scales delivered by TMA with the tile: widen each stage into tensor memory ----
+        if constexpr (FAM == FAM_W4A16) {
+          const bool bf16 = prm.bf16_act != 0;
+          for (int item = item0; item < n_items && ok; item += item_step) {
+            const Item w = decode_item<BQ, ATOMS>(prm, item);
+            for (int it = 0; it < w.ntiles && ok; ++it, ++g) {
+              const uint32_t s = g % S, st = stage0 + s * G::kStageBytes;
+              ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word);
+              if (ok && g >= 2) ok = mbar_wait(smem_u32(&hdr->a_empty[g & 1]), ((g >> 1) & 1) ^ 1, abort_word);
+              if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
+              tc_fence_after();
+              const uint32_t abuf = tmem + lane_addr + kABufCol + (g & 1u) * ATOMS * G::kAColsAtom;
+              if (bf16) w4_widen_stage<G, ATOMS, true>(st, abuf, r, part);
+              else w4_widen_stage<G, ATOMS, false>(st, abuf, r, part);
+              tmem_wait_st();
+              tc_fence_before();
+              mbar_arrive(smem_u32(&hdr->a_full[g & 1]));
+            }
+          }
+        }
+      } else if constexpr (G::kNvf4 || FAM == FAM_W4A16) {
         // Block scales travel by 4-byte cp.async (their rows are only 4-byte aligned); each thread moves the 16 scale
         // bytes per atom of "its" row and keeps up to kSfLag stages in flight.
         pdl_wait();
@@ -506,27 +613,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
               tc_fence_after();
               const uint32_t abuf = tmem + lane_addr + kABufCol + (gd & 1u) * ATOMS * G::kAColsAtom;
-#pragma unroll
-              for (int a = 0; a < ATOMS; ++a) {
-#pragma unroll
-                for (int cc = 0; cc < kChunks; ++cc) {
-                  const int c = part * kChunks + cc;
-                  // chunk c holds K [32c, 32c+32) of the atom = scale blocks 2c and 2c+1 = bytes 2c, 2c+1 of the row's 16
-                  uint32_t sc2;
-                  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sc2) : "r"(st + G::kSfAOff + a * 2048 + r * 16 + 2 * c));
-                  const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
-                  const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
-                  const uint32_t s0 = widen_scale(sc2 & 0xffu, bf16), s1 = widen_scale((sc2 >> 8) & 0xffu, bf16);
-#pragma unroll
-                  for (int h = 0; h < 2; ++h) {
-                    uint32_t o[8];
-#pragma unroll
-                    for (int b = 0; b < 8; ++b)
-                      o[b] = widen_e2m1x2((wv[h * 2 + b / 4] >> (8 * (b % 4))) & 0xffu, bf16, h ? s1 : s0);
-                    tmem_st8(abuf + a * G::kAColsAtom + c * 16 + h * 8, o);
-                  }
-                }
-              }
+              if (bf16) w4_widen_stage<G, ATOMS, true>(st, abuf, r, part);
+              else w4_widen_stage<G, ATOMS, false>(st, abuf, r, part);
               tmem_wait_st();
               tc_fence_before();
               mbar_arrive(smem_u32(&hdr->a_full[gd & 1]));
@@ -547,19 +635,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
             tc_fence_after();
             const uint32_t abuf = tmem + lane_addr + kABufCol + (g & 1u) * ATOMS * G::kAColsAtom;
-#pragma unroll
-            for (int a = 0; a < ATOMS; ++a)
-#pragma unroll
-              for (int cc = 0; cc < kChunks; ++cc) {
-                const int c = part * kChunks + cc;
-                const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
-                uint32_t o[8];
-                widen_e4m3x4(raw.x, bf16, o[0], o[1]);
-                widen_e4m3x4(raw.y, bf16, o[2], o[3]);
-                widen_e4m3x4(raw.z, bf16, o[4], o[5]);
-                widen_e4m3x4(raw.w, bf16, o[6], o[7]);
-                tmem_st8(abuf + a * G::kAColsAtom + c * 8, o);
-              }
+            if (bf16) w8_widen_stage<G, ATOMS, true>(st, abuf, r, part);
+            else w8_widen_stage<G, ATOMS, false>(st, abuf, r, part);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(smem_u32(&hdr->a_full[g & 1]));
@@ -620,6 +697,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (have_acc) {
           tmem_ld16(tmem + lane_addr + ab * G::kAccCols + c0, v);
           tmem_wait_ld();
+          if constexpr (FAM == FAM_W4A16) {
+            // bf16 activations: the widened weights carry a factor 2^-8 (see widen_e2m1x8); undone exactly here
+            if (prm.bf16_act) {
+#pragma unroll
+              for (int c = 0; c < 16; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * 256.f);
+            }
+          }
         } else {
 #pragma unroll
           for (int c = 0; c < 16; ++c) v[c] = 0u;
@@ -816,7 +900,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // host side
 
 template <int FAM, int BQ, int ATOMS>
-cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& prm, bool pdl, cudaStream_t stream) {
+cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& prm, bool pdl, cudaStream_t stream) {
   using G = Geo<FAM, BQ, ATOMS>;
   if constexpr (!G::kValid) {
     return cudaErrorInvalidConfiguration;
@@ -862,24 +946,24 @@ cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
       p.pdl_early = 1;  // one wave by construction: let the next kernel's CTAs take the SMs as they free up
     }
     return launch_ex(umma_gemm_kernel<FAM, BQ, ATOMS>, grid, dim3(G::kThreads), smem, stream, pdl,
-                     dim3(1, 1, p.cluster ? p.ksplit : 1), ta, tb, p);
+                     dim3(1, 1, p.cluster ? p.ksplit : 1), ta, tb, ts, p);
   }
 }
 
 template <int FAM>
-cudaError_t umma_launch_family(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int cfg, bool pdl,
+cudaError_t umma_launch_family(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl,
                                cudaStream_t s) {
   switch (cfg) {
-    case 0: return umma_launch_one<FAM, 16, 1>(ta, tb, p, pdl, s);
-    case 1: return umma_launch_one<FAM, 32, 1>(ta, tb, p, pdl, s);
-    case 2: return umma_launch_one<FAM, 64, 1>(ta, tb, p, pdl, s);
-    case 3: return umma_launch_one<FAM, 128, 1>(ta, tb, p, pdl, s);
-    case 4: return umma_launch_one<FAM, 256, 1>(ta, tb, p, pdl, s);
-    case 5: return umma_launch_one<FAM, 16, 2>(ta, tb, p, pdl, s);
-    case 6: return umma_launch_one<FAM, 32, 2>(ta, tb, p, pdl, s);
-    case 7: return umma_launch_one<FAM, 64, 2>(ta, tb, p, pdl, s);
-    case 8: return umma_launch_one<FAM, 128, 2>(ta, tb, p, pdl, s);
-    case 9: return umma_launch_one<FAM, 256, 2>(ta, tb, p, pdl, s);
+    case 0: return umma_launch_one<FAM, 16, 1>(ta, tb, ts, p, pdl, s);
+    case 1: return umma_launch_one<FAM, 32, 1>(ta, tb, ts, p, pdl, s);
+    case 2: return umma_launch_one<FAM, 64, 1>(ta, tb, ts, p, pdl, s);
+    case 3: return umma_launch_one<FAM, 128, 1>(ta, tb, ts, p, pdl, s);
+    case 4: return umma_launch_one<FAM, 256, 1>(ta, tb, ts, p, pdl, s);
+    case 5: return umma_launch_one<FAM, 16, 2>(ta, tb, ts, p, pdl, s);
+    case 6: return umma_launch_one<FAM, 32, 2>(ta, tb, ts, p, pdl, s);
+    case 7: return umma_launch_one<FAM, 64, 2>(ta, tb, ts, p, pdl, s);
+    case 8: return umma_launch_one<FAM, 128, 2>(ta, tb, ts, p, pdl, s);
+    case 9: return umma_launch_one<FAM, 256, 2>(ta, tb, ts, p, pdl, s);
     default: return cudaErrorInvalidValue;
   }
 }
