@@ -407,22 +407,27 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
       !make_map(&tb, a->b, a->b_row_bytes, Q, a->ldb_bytes, tile.bq, !p.a_is_weight))
     return fail(LLG_E_CUDA, "cuTensorMapEncodeTiled failed (operand layout not expressible as a TMA map)");
 
-  CUtensorMap ts = ta;  // only read when sf_tma is set
+  CUtensorMap ts = ta, tt = tb;  // only read when sf_tma is set
   p.sf_tma = 0;
-  if (tc_family_of(a->kind) == FAM_W4A16 && p.a_sf && p.lda_sf % 16 == 0 && aligned(p.a_sf, 16) &&
+  const int fam = tc_family_of(a->kind);
+  if (fam == FAM_W4A16 && p.a_sf && p.lda_sf % 16 == 0 && aligned(p.a_sf, 16) &&
       make_sf_map(&ts, p.a_sf, p.K / 16, P, p.lda_sf, p.p_rows))
+    p.sf_tma = 1;
+  if (fam == FAM_NVF4 && p.a_sf && p.b_sf && p.lda_sf % 16 == 0 && p.ldb_sf % 16 == 0 && aligned(p.a_sf, 16) &&
+      aligned(p.b_sf, 16) && make_sf_map(&ts, p.a_sf, p.K / 16, P, p.lda_sf, p.p_rows) &&
+      make_sf_map(&tt, p.b_sf, p.K / 16, Q, p.ldb_sf, tile.bq))
     p.sf_tma = 1;
 
   const bool pdl = pdl_on();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   switch (tc_family_of(a->kind)) {
-    case FAM_F16: e = tc_launch_f16(ta, tb, ts, p, a->cfg, pdl, s); break;
-    case FAM_F8: e = tc_launch_f8(ta, tb, ts, p, a->cfg, pdl, s); break;
-    case FAM_I8: e = tc_launch_i8(ta, tb, ts, p, a->cfg, pdl, s); break;
-    case FAM_NVF4: e = tc_launch_nvf4(ta, tb, ts, p, a->cfg, pdl, s); break;
-    case FAM_W8A16: e = tc_launch_w8a16(ta, tb, ts, p, a->cfg, pdl, s); break;
-    default: e = tc_launch_w4a16(ta, tb, ts, p, a->cfg, pdl, s); break;
+    case FAM_F16: e = tc_launch_f16(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
+    case FAM_F8: e = tc_launch_f8(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
+    case FAM_I8: e = tc_launch_i8(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
+    case FAM_NVF4: e = tc_launch_nvf4(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
+    case FAM_W8A16: e = tc_launch_w8a16(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
+    default: e = tc_launch_w4a16(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
   }
   if (e != cudaSuccess) {
     cudaGetLastError();

@@ -118,7 +118,7 @@ struct TcDev {
   int64_t pf_bytes;
   unsigned* status;
   unsigned char swap, bias_on_p, cluster, pdl_early, a_is_weight, bf16_act;
-  unsigned char sf_tma;  // W4A16: the block scales of A come by TMA (third tensor map) instead of per-thread copies
+  unsigned char sf_tma;  // W4A16 / NVFP4: block scales come by TMA (third and fourth tensor map), not per-thread copies
 };
 
 struct TcTile {
@@ -133,11 +133,11 @@ int tc_threads_of(int kind);  // 192, or 320 for the kinds with helper warps (bl
 constexpr int kSmemBudget = 227 * 1024 - 2048;  // dynamic shared memory for stages; the rest holds barriers and slack
 
 // Defined per family in umma_<family>.cu.
-cudaError_t tc_launch_f16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
-cudaError_t tc_launch_f8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
-cudaError_t tc_launch_i8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
-cudaError_t tc_launch_nvf4(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
-cudaError_t tc_launch_w8a16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
-cudaError_t tc_launch_w4a16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_f16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_f8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_i8(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_nvf4(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_w8a16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
+cudaError_t tc_launch_w4a16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl, cudaStream_t s);
 
 }  // namespace llg

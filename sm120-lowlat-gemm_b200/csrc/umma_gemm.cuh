@@ -291,7 +291,7 @@ __device__ __forceinline__ Item decode_item(const TcDev& prm, int item) {
 template <int FAM, int BQ, int ATOMS>
 __global__ void __launch_bounds__(Geo<FAM, BQ, ATOMS>::kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmS, const TcDev prm) {
+                 const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmT, const TcDev prm) {
   using G = Geo<FAM, BQ, ATOMS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_base = smem_u32(smem_raw);
@@ -331,7 +331,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
-    if (FAM == FAM_W4A16 && prm.sf_tma) tma_prefetch_desc(&tmS);
+    if ((FAM == FAM_W4A16 || G::kNvf4) && prm.sf_tma) tma_prefetch_desc(&tmS);
+    if (G::kNvf4 && prm.sf_tma) tma_prefetch_desc(&tmT);
   }
   if (prm.pdl_early) pdl_trigger();
   uint32_t tmem = 0;
@@ -364,16 +365,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
       // an A box holds p_rows rows (<= 128): the rows of the 128-row MMA tile below it keep stale data and produce
       // accumulator rows nobody reads
-      // W4A16 with 16-byte aligned scale rows: the 16 block-scale bytes per row and atom travel with the tile
-      const bool sf_tma = FAM == FAM_W4A16 && prm.sf_tma;
-      const uint32_t tx_bytes = (uint32_t)(ATOMS * prm.p_rows * (sf_tma ? 144 : 128)) + (uint32_t)G::kBBytes;
+      // block scales with 16-byte aligned rows: the 16 scale bytes per row and atom travel with the tile, as
+      // [row][16 bytes] boxes (W4A16 reads them as they are, NVFP4's helpers reorder them for the MMA)
+      const bool sf_tma = (FAM == FAM_W4A16 || G::kNvf4) && prm.sf_tma;
+      const uint32_t tx_bytes = (uint32_t)(ATOMS * prm.p_rows * (sf_tma ? 144 : 128)) + (uint32_t)G::kBBytes +
+                                (G::kNvf4 && sf_tma ? (uint32_t)(ATOMS * BQ * 16) : 0u);
       auto load_a = [&](const Item& w, int it, uint32_t g) {
         const uint32_t s = g % S, st = stage0 + s * G::kStageBytes, bar = smem_u32(&hdr->full[s]);
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a) {
           tma_load_2d(st + G::kAOff + a * kAAtomTile, &tmA, bar, ((w.kt_beg + it) * ATOMS + a) * kAtomBytes, w.p0,
                       a_first ? pol_w : pol_x);
-          if constexpr (FAM == FAM_W4A16) {
+          if constexpr (FAM == FAM_W4A16 || G::kNvf4) {
             if (sf_tma)
               tma_load_2d(st + G::kSfAOff + a * 2048, &tmS, bar, ((w.kt_beg + it) * ATOMS + a) * 16, w.p0,
                           a_first ? pol_w : pol_x);
@@ -386,6 +389,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int a = 0; a < ATOMS * G::kBPerA; ++a)
           tma_load_2d(st + G::kBOff + a * G::kBAtomTile, &tmB, bar,
                       ((w.kt_beg + it) * ATOMS * G::kBPerA + a) * kAtomBytes, w.q0, a_first ? pol_x : pol_w);
+        if constexpr (G::kNvf4) {
+          if (sf_tma) {
+#pragma unroll
+            for (int a = 0; a < ATOMS; ++a)
+              tma_load_2d(st + G::kSfBOff + a * 2048, &tmT, bar, ((w.kt_beg + it) * ATOMS + a) * 16, w.q0,
+                          a_first ? pol_x : pol_w);
+          }
+        }
       };
       uint32_t g = 0;
       bool ok = true, first = true;
@@ -487,6 +498,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             umma_commit(smem_u32(&hdr->a_empty[g & 1]));
           } else {
             const uint32_t sfc = tmem + kSfCol + (g & 1u) * G::kSfColsStage;
+            if constexpr (G::kNvf4) {
+              // every block-scale copy of the stage first (distinct columns), so the copies pipeline instead of each
+              // pair sitting directly in front of the MMA that needs it
+#pragma unroll
+              for (int i = 0; i < ATOMS * 4; ++i) {
+                const uint64_t sfo = (uint64_t)((s * G::kStageBytes + i * 512) >> 4);
+                tmem_cp_32x128b_x4(sfc + (uint32_t)i * 8, sfa0 + sfo);
+                tmem_cp_32x128b_x4(sfc + (uint32_t)i * 8 + 4, sfb0 + sfo);
+              }
+            }
 #pragma unroll
             for (int a = 0; a < ATOMS; ++a) {
               const uint64_t adesc = adesc0 + (uint64_t)((s * G::kStageBytes + a * kAAtomTile) >> 4);
@@ -499,9 +520,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 else if constexpr (FAM == FAM_I8) mma_ss_i8(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on);
                 else {
                   const uint32_t sfa_t = sfc + (uint32_t)(a * 4 + j) * 8, sfb_t = sfa_t + 4;
-                  const uint64_t sfo = (uint64_t)((s * G::kStageBytes + (a * 4 + j) * 512) >> 4);
-                  tmem_cp_32x128b_x4(sfa_t, sfa0 + sfo);
-                  tmem_cp_32x128b_x4(sfb_t, sfb0 + sfo);
                   mma_ss_nvf4(acc, adesc + 2 * j, bdesc + 2 * j, idesc, acc_on, sfa_t, sfb_t);
                 }
               }
@@ -545,6 +563,50 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tmem_wait_st();
               tc_fence_before();
               mbar_arrive(smem_u32(&hdr->a_full[g & 1]));
+            }
+          }
+        }
+      } else if (G::kNvf4 && prm.sf_tma) {
+        // ---- NVFP4, scales delivered by TMA as [row][16 bytes]: reorder them in place into the layout the MMA's
+        // scale copy reads - per MMA j a 512-byte block with row r at (r % 32) * 16 + (r / 32) * 4 ----
+        if constexpr (G::kNvf4) {
+          for (int item = item0; item < n_items && ok; item += item_step) {
+            const Item w = decode_item<BQ, ATOMS>(prm, item);
+            for (int it = 0; it < w.ntiles && ok; ++it, ++g) {
+              const uint32_t s = g % S, st = stage0 + s * G::kStageBytes;
+              ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word);
+              if (!ok) give_up(prm, ST_CONVERT_WAIT);
+              uint4 ra[ATOMS], rb[ATOMS];
+#pragma unroll
+              for (int a = 0; a < ATOMS; ++a) {
+                ra[a] = lds128(st + G::kSfAOff + a * 2048 + r * 16);
+                rb[a] = r < BQ ? lds128(st + G::kSfBOff + a * 2048 + r * 16) : make_uint4(0u, 0u, 0u, 0u);
+              }
+              // every row is read before any is overwritten; the barrier also makes the verdict of the wait common
+              // to the 128 helper threads, so they leave the loop together
+              {
+                uint32_t all_ok;
+                asm volatile(
+                    "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 2, 128, p;\n\t"
+                    "selp.u32 %0, 1, 0, q;\n\t}\n"
+                    : "=r"(all_ok)
+                    : "r"((uint32_t)ok)
+                    : "memory");
+                ok = all_ok != 0;
+              }
+              const uint32_t at = (uint32_t)((r & 31) * 16 + (r >> 5) * 4);
+#pragma unroll
+              for (int a = 0; a < ATOMS; ++a) {
+                const uint32_t da = st + G::kSfAOff + a * 2048 + at, db = st + G::kSfBOff + a * 2048 + at;
+                const uint32_t va[4] = {ra[a].x, ra[a].y, ra[a].z, ra[a].w}, vb[4] = {rb[a].x, rb[a].y, rb[a].z, rb[a].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  asm volatile("st.shared.u32 [%0], %1;" ::"r"(da + j * 512), "r"(va[j]) : "memory");
+                  asm volatile("st.shared.u32 [%0], %1;" ::"r"(db + j * 512), "r"(vb[j]) : "memory");
+                }
+              }
+              fence_async_shared();
+              mbar_arrive(smem_u32(&hdr->sf_full[s]));
             }
           }
         }
@@ -900,7 +962,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // host side
 
 template <int FAM, int BQ, int ATOMS>
-cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& prm, bool pdl, cudaStream_t stream) {
+cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& prm, bool pdl, cudaStream_t stream) {
   using G = Geo<FAM, BQ, ATOMS>;
   if constexpr (!G::kValid) {
     return cudaErrorInvalidConfiguration;
@@ -946,24 +1008,24 @@ cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
       p.pdl_early = 1;  // one wave by construction: let the next kernel's CTAs take the SMs as they free up
     }
     return launch_ex(umma_gemm_kernel<FAM, BQ, ATOMS>, grid, dim3(G::kThreads), smem, stream, pdl,
-                     dim3(1, 1, p.cluster ? p.ksplit : 1), ta, tb, ts, p);
+                     dim3(1, 1, p.cluster ? p.ksplit : 1), ta, tb, ts, tt, p);
   }
 }
 
 template <int FAM>
-cudaError_t umma_launch_family(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const TcDev& p, int cfg, bool pdl,
+cudaError_t umma_launch_family(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl,
                                cudaStream_t s) {
   switch (cfg) {
-    case 0: return umma_launch_one<FAM, 16, 1>(ta, tb, ts, p, pdl, s);
-    case 1: return umma_launch_one<FAM, 32, 1>(ta, tb, ts, p, pdl, s);
-    case 2: return umma_launch_one<FAM, 64, 1>(ta, tb, ts, p, pdl, s);
-    case 3: return umma_launch_one<FAM, 128, 1>(ta, tb, ts, p, pdl, s);
-    case 4: return umma_launch_one<FAM, 256, 1>(ta, tb, ts, p, pdl, s);
-    case 5: return umma_launch_one<FAM, 16, 2>(ta, tb, ts, p, pdl, s);
-    case 6: return umma_launch_one<FAM, 32, 2>(ta, tb, ts, p, pdl, s);
-    case 7: return umma_launch_one<FAM, 64, 2>(ta, tb, ts, p, pdl, s);
-    case 8: return umma_launch_one<FAM, 128, 2>(ta, tb, ts, p, pdl, s);
-    case 9: return umma_launch_one<FAM, 256, 2>(ta, tb, ts, p, pdl, s);
+    case 0: return umma_launch_one<FAM, 16, 1>(ta, tb, ts, tt, p, pdl, s);
+    case 1: return umma_launch_one<FAM, 32, 1>(ta, tb, ts, tt, p, pdl, s);
+    case 2: return umma_launch_one<FAM, 64, 1>(ta, tb, ts, tt, p, pdl, s);
+    case 3: return umma_launch_one<FAM, 128, 1>(ta, tb, ts, tt, p, pdl, s);
+    case 4: return umma_launch_one<FAM, 256, 1>(ta, tb, ts, tt, p, pdl, s);
+    case 5: return umma_launch_one<FAM, 16, 2>(ta, tb, ts, tt, p, pdl, s);
+    case 6: return umma_launch_one<FAM, 32, 2>(ta, tb, ts, tt, p, pdl, s);
+    case 7: return umma_launch_one<FAM, 64, 2>(ta, tb, ts, tt, p, pdl, s);
+    case 8: return umma_launch_one<FAM, 128, 2>(ta, tb, ts, tt, p, pdl, s);
+    case 9: return umma_launch_one<FAM, 256, 2>(ta, tb, ts, tt, p, pdl, s);
     default: return cudaErrorInvalidValue;
   }
 }
