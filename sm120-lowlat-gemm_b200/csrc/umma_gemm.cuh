@@ -39,6 +39,11 @@ struct Geo {
   // helper threads per tile row: the widening is ALU work, so several warps share each 32-lane quarter of tensor memory
   static constexpr int kParts = FAM == FAM_W4A16 ? 4 : FAM == FAM_W8A16 ? 2 : 1;
   static constexpr int kHelperThreads = kHelpers ? 128 * kParts : 0;
+  // the converter warps of the mixed kinds form two groups that take alternate stages (each owns one of the two widened
+  // A buffers), so the waits and the store latency of one stage overlap the arithmetic of the next; within a group
+  // kSubParts threads share a row
+  static constexpr int kGroups = kMixed ? 2 : 1;
+  static constexpr int kSubParts = kParts / kGroups;
   static constexpr int kThreads = 192 + kHelperThreads;
   static constexpr int kBPerA = FAM == FAM_W8A16 ? 2 : FAM == FAM_W4A16 ? 4 : 1;  // B atoms per A atom
   static constexpr int kBAtomTile = BQ * 128;
@@ -193,7 +198,7 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // widened into 8 columns (2 K per column) of the thread's lane of tensor memory.
 template <class G, int ATOMS, bool BF16>
 __device__ __forceinline__ void w8_widen_stage(uint32_t st, uint32_t abuf, int r, int part) {
-  constexpr int kChunks = 8 / G::kParts;
+  constexpr int kChunks = 8 / G::kSubParts;
 #pragma unroll
   for (int a = 0; a < ATOMS; ++a)
 #pragma unroll
@@ -214,7 +219,7 @@ __device__ __forceinline__ void w8_widen_stage(uint32_t st, uint32_t abuf, int r
 // [part * kChunks, +kChunks) and writes them, widened and scaled, to its lane of tensor memory (2 K per column).
 template <class G, int ATOMS, bool BF16>
 __device__ __forceinline__ void w4_widen_stage(uint32_t st, uint32_t abuf, int r, int part) {
-  constexpr int kChunks = 8 / G::kParts;
+  constexpr int kChunks = 8 / G::kSubParts;
   static_assert(kChunks % 2 == 0, "scales are fetched four at a time");
 #pragma unroll
   for (int a = 0; a < ATOMS; ++a) {
@@ -323,7 +328,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&hdr->acc_full[b]), 1);
       mbar_init(smem_u32(&hdr->acc_empty[b]), 128);
-      mbar_init(smem_u32(&hdr->a_full[b]), G::kMixed ? G::kHelperThreads : 128);
+      mbar_init(smem_u32(&hdr->a_full[b]), G::kMixed ? G::kHelperThreads / G::kGroups : 128);
       mbar_init(smem_u32(&hdr->a_empty[b]), 1);
     }
     hdr->abort = 0u;
@@ -540,8 +545,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int ht = tid - 192;                // 0..kHelperThreads-1
       const int quarter = warp & 3;            // tensor-memory lanes this warp may touch: [32*quarter, +32)
       const int r = quarter * 32 + lane;       // row of the tile this thread works on
-      const int part = (warp - 6) >> 2;        // which share of the row's 16-byte chunks (mixed kinds)
-      constexpr int kChunks = 8 / G::kParts;   // 16-byte chunks of a 128-byte row per thread
+      const int group = ((warp - 6) >> 2) % G::kGroups;  // mixed kinds: stages g with g % 2 == group are this thread's
+      const int part = ((warp - 6) >> 2) / G::kGroups;   // which share of the row's 16-byte chunks within the group
       const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
       bool ok = true;
       uint32_t g = 0;
@@ -552,6 +557,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int item = item0; item < n_items && ok; item += item_step) {
             const Item w = decode_item<BQ, ATOMS>(prm, item);
             for (int it = 0; it < w.ntiles && ok; ++it, ++g) {
+              if ((int)(g & 1u) != group) continue;
               const uint32_t s = g % S, st = stage0 + s * G::kStageBytes;
               ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word);
               if (ok && g >= 2) ok = mbar_wait(smem_u32(&hdr->a_empty[g & 1]), ((g >> 1) & 1) ^ 1, abort_word);
@@ -628,7 +634,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int item = item0; item < n_items && ok; item += item_step) {
           const Item w = decode_item<BQ, ATOMS>(prm, item);
           for (int it = 0; it < w.ntiles + lag && ok; ++it) {
-            if (it < w.ntiles) {
+            // W4A16: only the stages of this thread's group (an empty copy group keeps the count per iteration)
+            if (it < w.ntiles && (!G::kMixed || (int)((g + (uint32_t)it) & 1u) == group)) {
               const uint32_t gi = g + (uint32_t)it, s = gi % S, st = stage0 + s * G::kStageBytes;
               if (gi >= (uint32_t)S) ok = mbar_wait(smem_u32(&hdr->empty[s]), ((gi / S) & 1) ^ 1, abort_word);
               if (!ok) { give_up(prm, ST_CONVERT_WAIT); break; }
@@ -638,7 +645,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const int sfk = sfk0 + j * 4;
-                  if (FAM == FAM_W4A16 && (j * G::kParts) / 4 != part) continue;  // another thread of this row owns the piece
+                  if (FAM == FAM_W4A16 && (j * G::kSubParts) / 4 != part) continue;  // another thread of this row owns the piece
                   {
                     const bool v = w.p0 + r < prm.P && sfk < sfk_total;
                     const unsigned char* src = v ? prm.a_sf + (int64_t)(w.p0 + r) * prm.lda_sf + sfk : prm.a_sf;
@@ -663,6 +670,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             else if (lag == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
             else asm volatile("cp.async.wait_group 1;" ::: "memory");
             const uint32_t gd = g + (uint32_t)done, s = gd % S;
+            if (G::kMixed && (int)(gd & 1u) != group) continue;
             if constexpr (G::kNvf4) {
               fence_async_shared();
               mbar_arrive(smem_u32(&hdr->sf_full[s]));
@@ -691,6 +699,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int item = item0; item < n_items && ok; item += item_step) {
           const Item w = decode_item<BQ, ATOMS>(prm, item);
           for (int it = 0; it < w.ntiles && ok; ++it, ++g) {
+            if ((int)(g & 1u) != group) continue;
             const uint32_t s = g % S, st = stage0 + s * G::kStageBytes;
             ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word);
             if (ok && g >= 2) ok = mbar_wait(smem_u32(&hdr->a_empty[g & 1]), ((g >> 1) & 1) ^ 1, abort_word);
