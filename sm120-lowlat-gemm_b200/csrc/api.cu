@@ -127,6 +127,14 @@ int sm_count() {
   return counts[dev];
 }
 
+int64_t l2_bytes() {
+  static int sizes[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (sizes[dev] == 0) cudaDeviceGetAttribute(&sizes[dev], cudaDevAttrL2CacheSize, dev);
+  return sizes[dev];
+}
+
 unsigned int* status_word_device_ptr() {
   static unsigned int* ptrs[64] = {};
   int dev = 0;

@@ -24,6 +24,7 @@ unsigned int* status_word_device_ptr();  // device address of the status word of
 // ---- process-wide switches / caches --------------------------------------------------------------------------
 bool pdl_on();
 int sm_count();
+int64_t l2_bytes();  // L2 cache size of the current device
 
 // Launch with optional PDL attribute and cluster shape.
 template <typename... KArgs, typename... Args>
@@ -118,6 +119,8 @@ struct TcDev {
   int64_t pf_bytes;
   unsigned* status;
   unsigned char swap, bias_on_p, cluster, pdl_early, a_is_weight, bf16_act;
+  int pf_pace;          // > 0: self-prefetch of later weight stages into L2, one stage per pf_pace cycles
+  int pf_ahead;         // ... at most this many stages ahead of the producer
   unsigned char sf_tma;  // W4A16 / NVFP4: block scales come by TMA (third and fourth tensor map), not per-thread copies
 };
 

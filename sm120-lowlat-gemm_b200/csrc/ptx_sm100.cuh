@@ -99,6 +99,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // ---------------------------------------------------------------------------------------------------------------
 // TMA: 2-D tiled load into this CTA's shared memory, completion counted on an mbarrier (no multicast anywhere)
 
+// Bring one box of a tiled map into L2 only (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(m), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
 }

@@ -79,6 +79,7 @@ struct SmemHeader {
   uint32_t abort;
   uint32_t last;
   uint32_t trace_slot;
+  uint32_t prod_stage;               // first item: stages the producer has issued (0 until the dependency resolved)
 };
 static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header too large");
 
@@ -332,6 +333,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(smem_u32(&hdr->a_empty[b]), 1);
     }
     hdr->abort = 0u;
+    hdr->prod_stage = 0u;
     hdr->last = 0u;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -429,6 +431,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           it = npre;
           g = (uint32_t)npre;
           first = false;
+          if (prm.pf_pace > 0 && leader) *reinterpret_cast<volatile uint32_t*>(&hdr->prod_stage) = (uint32_t)npre;
         }
         for (; it < w.ntiles; ++it, ++g) {
           const uint32_t s = g % S;
@@ -440,6 +443,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             mbar_expect_tx(smem_u32(&hdr->full[s]), tx_bytes);
             load_a(w, it, g);
             load_b(w, it, g);
+            if (prm.pf_pace > 0 && item == item0) *reinterpret_cast<volatile uint32_t*>(&hdr->prod_stage) = (uint32_t)(it + 1);
           }
         }
       }
@@ -724,6 +728,37 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t parked = stage0;          // cluster split-K: [BQ][128] 4-byte partials, q-major
     bool ok = true;
     uint32_t n_acc = 0;
+    if (prm.pf_pace > 0 && warp == 2 && a_first && item0 < n_items) {
+      // While the epilogue has nothing to do, one lane walks ahead of the producer and asks for the weight tiles of
+      // the first item's later stages to be brought into L2, one stage per pf_pace cycles. A CTA that is resident
+      // before the previous kernel has finished thus keeps the memory system busy through the hand-over, and its
+      // producer later finds the tiles in L2. Every wait here is on the clock, so the loop is bounded.
+      if (elect_one()) {
+        const Item w = decode_item<BQ, ATOMS>(prm, item0);
+        const long long t0 = clock64(), pace = prm.pf_pace;
+        int k = S;
+        while (k < w.ntiles) {
+          const int prod = (int)*reinterpret_cast<volatile uint32_t*>(&hdr->prod_stage);
+          if (prod + 1 >= w.ntiles) break;
+          if (k <= prod + 1) k = prod + 2;  // the producer has caught up: stay a little ahead of it
+          if (k >= w.ntiles || clock64() - t0 > kWaitCycles) break;
+          // not further ahead of the producer than the L2 share this CTA may fill, and not faster than the pace
+          if (k > (prod > S ? prod : S) + prm.pf_ahead || clock64() - t0 < (long long)(k - S + 1) * pace) {
+            __nanosleep(64);
+            continue;
+          }
+#pragma unroll
+          for (int a = 0; a < ATOMS; ++a) {
+            tma_prefetch_2d(&tmA, ((w.kt_beg + k) * ATOMS + a) * kAtomBytes, w.p0);
+            if constexpr (FAM == FAM_W4A16 || G::kNvf4) {
+              if (prm.sf_tma) tma_prefetch_2d(&tmS, ((w.kt_beg + k) * ATOMS + a) * 16, w.p0);
+            }
+          }
+          ++k;
+        }
+      }
+      __syncwarp();
+    }
     pdl_wait();
     const float alpha = prm.alpha_ptr ? prm.alpha * __ldg(prm.alpha_ptr) : prm.alpha;
     for (int item = item0; item < n_items; item += item_step) {
@@ -1002,6 +1037,7 @@ cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
     if (p.cluster) {
       if (tiles > INT32_MAX) return cudaErrorInvalidValue;
       p.n_items = 1;
+      p.pf_pace = 0;
       grid = dim3((unsigned)tiles, 1, p.ksplit);
       p.pdl_early = tiles * p.ksplit <= sm_count();
     } else {
@@ -1015,6 +1051,19 @@ cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
       const int64_t resident = (int64_t)sm_count() * occ;
       grid = dim3((unsigned)(items < resident ? items : resident), 1, 1);
       p.pdl_early = 1;  // one wave by construction: let the next kernel's CTAs take the SMs as they free up
+      // Self-prefetch pace (see the kernel's epilogue warps): one stage of weights per CTA every so many cycles that
+      // all CTAs together ask for about what the memory delivers, kHbmBytesPerCycle (about 5 TB/s at 1.9 GHz; asking faster measured slower).
+      // Only in a chain of dependent launches, with the weights on the streamed side and one item per CTA.
+      // Only when everything beyond the ring fits the part of L2 that the running kernel's own stream can spare
+      // (0.4 of it): a larger weight would be fetched half by request and half ahead, and that measured slower than
+      // no prefetch at all.
+      constexpr int64_t kHbmBytesPerCycle = 2600;
+      const int64_t stage_w = (int64_t)ATOMS * 128 * p.p_rows, nk = (p.k_atoms + ATOMS - 1) / ATOMS;
+      const int64_t ahead = nk > p.stages ? nk - p.stages : 0;
+      const bool fits = ahead * stage_w * grid.x <= l2_bytes() * 2 / 5;
+      p.pf_pace = (pdl && p.a_is_weight && p.ksplit == 1 && items <= resident && ahead > 0 && fits)
+                      ? (int)(stage_w * grid.x / kHbmBytesPerCycle) : 0;
+      p.pf_ahead = (int)ahead;
     }
     return launch_ex(umma_gemm_kernel<FAM, BQ, ATOMS>, grid, dim3(G::kThreads), smem, stream, pdl,
                      dim3(1, 1, p.cluster ? p.ksplit : 1), ta, tb, ts, tt, p);
