@@ -342,10 +342,25 @@ def run_tp(args) -> None:
     _progress("process group up")
     L.set_pdl(not args.no_pdl)
     layers = args.layers
-    comm = None
-    if args.allreduce == "oneshot" and multi:
+    comm, comm_note = None, ("nccl all_reduce" if multi else "none (one rank)")
+    if args.allreduce in ("auto", "oneshot") and multi:
+        # the library's own one-shot all-reduce over peer memory; "auto" falls back to NCCL on every rank together
+        # when the peer mappings cannot be set up on any of them
         from lowlat_gemm import comm as CM
-        comm = CM.OneShotAllReduce(None, dev, max_bytes=TP_M * 8192 * 2, ctas=16)
+        try:
+            comm = CM.OneShotAllReduce(None, dev, max_bytes=TP_M * 8192 * 2, ctas=16)
+            failed = ""
+        except Exception as exc:  # noqa: BLE001 - any setup failure means "use NCCL"
+            if args.allreduce == "oneshot":
+                raise
+            failed = type(exc).__name__
+        flag = torch.tensor([0 if failed else 1], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            comm_note = "one-shot peer-memory all-reduce"
+        else:
+            comm = None
+            comm_note = "nccl all_reduce (peer-memory setup failed" + (f": {failed})" if failed else " on another rank)")
     step = TP.DecodeStep(TP_KIND, layers, world, rank, dev, prefetch_bytes=0, comm=comm)
     _progress("weights built")
     x = torch.randn(TP_M, step.shape.hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(1)).to(torch.bfloat16) * 0.05
@@ -412,7 +427,7 @@ def run_tp(args) -> None:
                 "scaling": "strong", "vs_baseline": None, "dtype": "fp8", "data": "synthetic",
                 "config": {"workload": "c5_tp_decode_step", "hidden": 8192, "qkv": 10240, "gate_up": 57344, "down": 28672,
                            "tokens": TP_M, "layers": layers, "parallelism": f"tp{world}",
-                           "collective": ("one-shot peer-memory all-reduce" if comm is not None else "nccl all_reduce") + " x2 per layer",
+                           "collective": comm_note + " x2 per layer",
                            "us_per_layer": ms * 1e3 / args.steps / layers, "pdl": L.pdl_enabled(), "launch": "cuda_graph",
                            "cold_weights": f"{layers} layers of distinct weights ({step.weight_bytes() >> 20} MB per rank)"},
                 "e2e": {"value": total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
@@ -445,7 +460,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--layers", type=int, default=8)
-    ap.add_argument("--allreduce", choices=("nccl", "oneshot"), default="nccl")
+    ap.add_argument("--allreduce", choices=("auto", "nccl", "oneshot"), default="auto")
     ap.add_argument("--workload", choices=("auto", "c2", "c5"), default="auto",
                     help="auto: config 2 on one GPU, config 5 (tensor-parallel decode step) on several")
     args = ap.parse_args()

@@ -181,6 +181,18 @@ LLG_API int llg_device_status(uint32_t* status);
 LLG_API int llg_allreduce_oneshot(const void* const* buffers_dev, uint32_t* const* flags_dev, void* out, int64_t bytes,
                                   int32_t dtype, int32_t rank, int32_t world, int32_t ctas, void* stream);
 
+/* The same all-reduce followed, in the same kernel, by the per-token FP8 activation quantizer
+ * (lowlat_gemm/__init__.py:quantize_fp8, csrc/quant.cu:43-66 of the reference): the partials are [rows, cols] 16-bit
+ * values, contiguous, at the start of every rank's buffer; one CTA and one flag set per row, so rows <= LLG_AR_MAX_CTAS
+ * and the flag words must hold rows * world entries; cols a multiple of 8, at most LLG_ARQ_MAX_COLS. Writes
+ * q [rows, ldq] (e4m3 bytes) and scale_out [rows] = max(amax / 448, min_scale), bit-identical to quantize_fp8 applied
+ * to the all-reduce's 16-bit result, and that result itself to `out` unless out is NULL. Same buffer alternation,
+ * flag and bounded-wait rules as llg_allreduce_oneshot. No counterpart in the reference. */
+#define LLG_ARQ_MAX_COLS 16384
+LLG_API int llg_allreduce_quant_fp8(const void* const* buffers_dev, uint32_t* const* flags_dev, void* out, void* q,
+                                    int64_t ldq, float* scale_out, int32_t rows, int32_t cols, int32_t dtype,
+                                    float min_scale, int32_t rank, int32_t world, void* stream);
+
 /* Split-K tensor-core GEMM for callers that must not allocate device memory. Same arguments and result as
  * llg_tc_gemm, except that args->ws / args->counters are ignored: partial sums and arrival counters live in a fixed
  * scratch array inside the library (LLG_STATIC_WS_ELEMS 4-byte partials + LLG_STATIC_COUNTERS counters, about 4 MB,

@@ -120,7 +120,123 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArD
   }
 }
 
+// ---- all-reduce fused with the per-token FP8 quantizer --------------------------------------------------------------
+// One CTA per row (token): the row's partials are added in rank order in fp32 and rounded to the activation type -
+// the very values the stand-alone all-reduce would have stored - and the quantizer's arithmetic follows on them in
+// registers (scale = max(amax / 448, min_scale), IEEE division for the scale and its reciprocal, one multiply per
+// element, cvt.rn.satfinite.e4m3x2), so (q, scale) equal quantize_fp8(all_reduce(x)) bit for bit while one kernel and
+// one dependent launch disappear from the chain. The rounded sum itself is stored too when the caller asks for it.
+constexpr int kArqThreads = 1024, kArqUnits = 2;  // rows up to 1024 * 2 * 8 = 16384 elements
+
+struct ArqDev {
+  const void* const* buffers;
+  uint32_t* const* flags;
+  void* out;             // optional [rows, cols] rounded sum (same type as the partials), may be null
+  unsigned char* q;      // [rows, ldq] e4m3 bytes
+  float* scale_out;      // [rows]
+  int64_t ldq;
+  int cols, rank, world;
+  float min_scale;
+  unsigned* status;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(kArqThreads) allreduce_quant_fp8_kernel(const ArqDev p) {
+  const int tid = threadIdx.x, row = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[kArqThreads / 32];
+  if (tid < p.world) {
+    __threadfence_system();
+    bool ok = flag_send(p.flags[tid] + (int64_t)row * p.world + p.rank);
+    ok = flag_recv(p.flags[p.rank] + (int64_t)row * p.world + tid) && ok;
+    __threadfence_system();
+    if (!ok) atomicCAS(p.status, 0u, 16u);
+  }
+  __syncthreads();
+  const int units = p.cols >> 3;  // 8 values = 16 bytes per unit
+  float r[kArqUnits][8];
+  float a = 0.f;
+#pragma unroll
+  for (int j = 0; j < kArqUnits; ++j) {
+    const int u = tid + j * kArqThreads;
+    if (u < units) {
+      const int64_t i = (int64_t)row * units + u;
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k < p.world) v[k] = __ldcv(static_cast<const uint4*>(p.buffers[k]) + i);
+      float acc[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k < p.world) accumulate<DT>(acc, v[k], k == 0);
+      uint4 o;
+      if constexpr (DT == LLG_DT_BF16) {
+        __nv_bfloat162 t[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) t[e] = __halves2bfloat162(__float2bfloat16_rn(acc[2 * e]), __float2bfloat16_rn(acc[2 * e + 1]));
+        o = *reinterpret_cast<const uint4*>(t);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          r[j][2 * e] = __bfloat162float(t[e].x);
+          r[j][2 * e + 1] = __bfloat162float(t[e].y);
+        }
+      } else {
+        __half2 t[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) t[e] = __halves2half2(__float2half_rn(acc[2 * e]), __float2half_rn(acc[2 * e + 1]));
+        o = *reinterpret_cast<const uint4*>(t);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(t[e]);
+          r[j][2 * e] = f.x;
+          r[j][2 * e + 1] = f.y;
+        }
+      }
+      if (p.out) static_cast<uint4*>(p.out)[i] = o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a = fmaxf(a, fabsf(r[j][e]));
+    }
+  }
+  // row maximum over the CTA
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, d));
+  if ((tid & 31) == 0) red[tid >> 5] = a;
+  __syncthreads();
+  a = red[tid & 31];  // kArqThreads / 32 == 32 partial maxima
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, d));
+  const float scale = fmaxf(__fdiv_rn(a, 448.f), p.min_scale);
+  if (tid == 0) p.scale_out[row] = scale;
+  const float inv = __fdiv_rn(1.f, scale);
+  unsigned char* const q = p.q + (int64_t)row * p.ldq;
+#pragma unroll
+  for (int j = 0; j < kArqUnits; ++j) {
+    const int u = tid + j * kArqThreads;
+    if (u < units) {
+      const uint32_t w0 = cvt_e4m3x2(__fmul_rn(r[j][0], inv), __fmul_rn(r[j][1], inv)) |
+                          (cvt_e4m3x2(__fmul_rn(r[j][2], inv), __fmul_rn(r[j][3], inv)) << 16);
+      const uint32_t w1 = cvt_e4m3x2(__fmul_rn(r[j][4], inv), __fmul_rn(r[j][5], inv)) |
+                          (cvt_e4m3x2(__fmul_rn(r[j][6], inv), __fmul_rn(r[j][7], inv)) << 16);
+      *reinterpret_cast<uint2*>(q + u * 8) = make_uint2(w0, w1);
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t allreduce_quant_fp8_launch(const void* const* buffers, uint32_t* const* flags, void* out, void* q, int64_t ldq,
+                                       float* scale_out, int rows, int cols, int dtype, float min_scale, int rank,
+                                       int world, unsigned* status, cudaStream_t s) {
+  ArqDev p{buffers, flags, out, static_cast<unsigned char*>(q), scale_out, ldq, cols, rank, world, min_scale, status};
+  const bool pdl = pdl_on();
+  const dim3 grid(rows), block(kArqThreads), one(1, 1, 1);
+  switch (dtype) {
+    case LLG_DT_BF16: return launch_ex(allreduce_quant_fp8_kernel<LLG_DT_BF16>, grid, block, 0, s, pdl, one, p);
+    case LLG_DT_F16: return launch_ex(allreduce_quant_fp8_kernel<LLG_DT_F16>, grid, block, 0, s, pdl, one, p);
+    default: return cudaErrorInvalidValue;
+  }
+}
 
 cudaError_t allreduce_launch(const void* const* buffers, uint32_t* const* flags, void* out, int64_t vecs, int rank,
                              int world, int dtype, int ctas, unsigned* status, cudaStream_t s) {

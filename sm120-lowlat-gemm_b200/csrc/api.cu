@@ -465,6 +465,31 @@ int llg_allreduce_oneshot(const void* const* buffers_dev, uint32_t* const* flags
   return LLG_OK;
 }
 
+int llg_allreduce_quant_fp8(const void* const* buffers_dev, uint32_t* const* flags_dev, void* out, void* q, int64_t ldq,
+                            float* scale_out, int32_t rows, int32_t cols, int32_t dtype, float min_scale, int32_t rank,
+                            int32_t world, void* stream) {
+  if (!buffers_dev || !flags_dev || !q || !scale_out) return fail(LLG_E_INVALID, "all-reduce + quantize: null pointer");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(LLG_E_INVALID, "all-reduce: world must be in [1, 8] and rank inside it, got rank %d of %d", rank, world);
+  if (rows < 1 || rows > LLG_AR_MAX_CTAS)
+    return fail(LLG_E_INVALID, "all-reduce + quantize: rows must be in [1, %d] (one CTA and one flag set per row), got %d",
+                LLG_AR_MAX_CTAS, rows);
+  if (cols < 8 || cols % 8 || cols > LLG_ARQ_MAX_COLS)
+    return fail(LLG_E_INVALID, "all-reduce + quantize: cols must be a multiple of 8 in [8, %d], got %d", LLG_ARQ_MAX_COLS, cols);
+  if (dtype != LLG_DT_BF16 && dtype != LLG_DT_F16) return fail(LLG_E_INVALID, "all-reduce + quantize: dtype must be bf16 or f16");
+  if (ldq < cols || ldq % 8 || !aligned(q, 8) || (out && !aligned(out, 16)))
+    return fail(LLG_E_INVALID, "all-reduce + quantize: q needs 8-byte aligned rows (ldq %% 8 == 0, ldq >= cols), out 16-byte alignment");
+  unsigned* status = status_word_device_ptr();
+  if (!status) return fail(LLG_E_CUDA, "no device status word");
+  const cudaError_t e = allreduce_quant_fp8_launch(buffers_dev, flags_dev, out, q, ldq, scale_out, rows, cols, dtype,
+                                                   min_scale, rank, world, status, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LLG_E_CUDA, "all-reduce + quantize launch failed: %s", cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
 int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream) {
   if (!args) return fail(LLG_E_INVALID, "null arguments");
   // set-up, once per device, with that device current: the device address of the scratch array

@@ -75,6 +75,9 @@ cudaError_t skinny_launch_l32(const SkinnyDev& p, int rows, int unroll, int warp
 // ---- one-shot all-reduce over peer memory ------------------------------------------------------------------------
 cudaError_t allreduce_launch(const void* const* buffers, uint32_t* const* flags, void* out, int64_t vecs, int rank,
                              int world, int dtype, int ctas, unsigned* status, cudaStream_t s);
+cudaError_t allreduce_quant_fp8_launch(const void* const* buffers, uint32_t* const* flags, void* out, void* q, int64_t ldq,
+                                       float* scale_out, int rows, int cols, int dtype, float min_scale, int rank,
+                                       int world, unsigned* status, cudaStream_t s);
 
 // ---- quantizers --------------------------------------------------------------------------------------------------
 struct GatedExtra {

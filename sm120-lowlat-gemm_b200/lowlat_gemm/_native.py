@@ -64,6 +64,8 @@ SYMBOLS = {
     "llg_set_pdl": (None, [c_i32]),
     "llg_pdl_enabled": (c_i32, []),
     "llg_allreduce_oneshot": (c_i32, [c_ptr, c_ptr, c_ptr, c_i64, c_i32, c_i32, c_i32, c_i32, c_ptr]),
+    "llg_allreduce_quant_fp8": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i32, c_i32, c_i32, C.c_float, c_i32,
+                                        c_i32, c_ptr]),
     "llg_tc_gemm_static_ws": (c_i32, [C.POINTER(TcArgs), c_ptr]),
     "llg_tc_gemm_host": (c_i32, [C.POINTER(TcArgs), c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_ptr]),
     "llg_device_status": (c_i32, [C.POINTER(C.c_uint32)]),
@@ -72,6 +74,7 @@ SYMBOLS = {
     "llg_abi_version": (c_i32, []),
 }
 ABI_VERSION = 1
+AR_MAX_CTAS = 64      # LLG_AR_MAX_CTAS: flag sets (CTAs, or rows of the fused all-reduce + quantizer) per all-reduce
 
 
 def library_path() -> Path:

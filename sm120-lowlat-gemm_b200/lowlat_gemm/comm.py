@@ -32,7 +32,7 @@ class OneShotAllReduce:
             raise ValueError("one-shot all-reduce supports at most 8 ranks")
         self.device, self.ctas, self.max_bytes = device, ctas, (max_bytes + 15) // 16 * 16
         self.bufs = [symm.empty(self.max_bytes, dtype=torch.uint8, device=device) for _ in range(buffers)]
-        self.flags = symm.empty(ctas * self.world, dtype=torch.int32, device=device)
+        self.flags = symm.empty(max(ctas, N.AR_MAX_CTAS) * self.world, dtype=torch.int32, device=device)
         self.flags.zero_()
         handles = [symm.rendezvous(b, self.group) for b in self.bufs]
         fh = symm.rendezvous(self.flags, self.group)
@@ -64,3 +64,20 @@ class OneShotAllReduce:
                 C.c_void_p(out.data_ptr()), nbytes, _DT[out.dtype], self.rank, self.world, self.ctas,
                 C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
         return out
+
+    def reduce_quantize_fp8(self, index: int, rows: int, cols: int, dtype: torch.dtype, out: torch.Tensor | None = None,
+                            min_scale: float = 1e-12):
+        """(q, scale) = quantize_fp8(sum over ranks of buffer `index`), one kernel (`llg_allreduce_quant_fp8`): the
+        16-bit sum is formed and quantized in registers, bit-identical to reduce() followed by quantize_fp8(). With
+        `out` ([rows, cols], contiguous, `dtype`) the 16-bit sum is stored as well. rows <= 64, cols % 8 == 0."""
+        q = torch.empty(rows, cols, device=self.device, dtype=torch.float8_e4m3fn)
+        scale = torch.empty(rows, device=self.device, dtype=torch.float32)
+        if out is not None and (not out.is_contiguous() or out.dtype != dtype or tuple(out.shape) != (rows, cols)):
+            raise ValueError("out must be a contiguous [rows, cols] tensor of the partials' dtype")
+        with torch.cuda.device(self.device):
+            N.check(N.lib.llg_allreduce_quant_fp8(
+                C.c_void_p(self._buf_ptrs[index % len(self.bufs)].data_ptr()), C.c_void_p(self._flag_ptrs.data_ptr()),
+                C.c_void_p(out.data_ptr() if out is not None else 0), C.c_void_p(q.data_ptr()), q.stride(0),
+                C.c_void_p(scale.data_ptr()), rows, cols, _DT[dtype], float(min_scale), self.rank, self.world,
+                C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+        return q, scale

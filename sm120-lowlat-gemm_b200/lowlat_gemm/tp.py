@@ -81,7 +81,7 @@ class DecodeStep:
     """`layers` decode layers on this rank; run() executes them in order on the current stream."""
 
     def __init__(self, kind: str, layers: int, tp: int, rank: int, device, shape: LayerShape = LayerShape(), group=None,
-                 gemm_fn=None, prefetch_bytes: int = 0, nvfp4_global: float = 64.0, comm=None):
+                 gemm_fn=None, prefetch_bytes: int = 0, nvfp4_global: float = 64.0, comm=None, fuse_quant: bool = True):
         self.kind, self.tp, self.rank, self.group, self.device = kind, tp, rank, group, device
         self.shape = shape
         self.layers = [DecodeLayer(kind, shape, tp, rank, device, seed=i) for i in range(layers)]
@@ -95,6 +95,7 @@ class DecodeStep:
         self.gemms = 0
         self.comm = comm if tp > 1 else None  # a comm.OneShotAllReduce, or None for NCCL all_reduce
         self._ar_index = 0
+        self.fuse_quant = fuse_quant  # FP8 with `comm`: all-reduce and the next activation quantizer as one kernel
 
     def weight_bytes(self) -> int:
         return sum(l.weight_bytes() for l in self.layers)
@@ -109,6 +110,9 @@ class DecodeStep:
         if nxt is not None and self.prefetch_bytes:
             extra.update(prefetch=nxt, prefetch_bytes=min(self.prefetch_bytes, nxt.numel() * nxt.element_size()))
         self.gemms += 1
+        if isinstance(h, tuple):  # (q, scale): already quantized by the fused all-reduce of the previous projection
+            q, s = h
+            return self._gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
         if gated and self._api is None:  # host stand-in used by the CPU tests
             half = h.shape[1] // 2
             h, gated = torch.nn.functional.silu(h[:, :half]) * h[:, half:], False
@@ -122,8 +126,10 @@ class DecodeStep:
             h = self._api.silu_mul(h)
         return self._gemm(h, w, out_dtype=self.act_dtype, **kw, **extra)
 
-    def _row_parallel(self, h: torch.Tensor, w, kw: dict, nxt, gated: bool = False) -> torch.Tensor:
-        """Row-parallel projection followed by the sum over ranks."""
+    def _row_parallel(self, h: torch.Tensor, w, kw: dict, nxt, gated: bool = False, feeds_gemm: bool = False):
+        """Row-parallel projection followed by the sum over ranks. With `feeds_gemm` (the sum only feeds the next FP8
+        projection) and the library's own all-reduce, the sum and that projection's activation quantizer run as one
+        kernel and the result is the (q, scale) pair."""
         if self.tp == 1:
             return self._project(h, w, kw, nxt, gated=gated)
         self.collectives += 1
@@ -133,7 +139,10 @@ class DecodeStep:
             return y
         idx = self._ar_index
         self._ar_index += 1
-        part = self._project(h, w, kw, nxt, out=self.comm.view(idx, (h.shape[0], w.shape[0]), self.act_dtype), gated=gated)
+        rows = h[0].shape[0] if isinstance(h, tuple) else h.shape[0]
+        part = self._project(h, w, kw, nxt, out=self.comm.view(idx, (rows, w.shape[0]), self.act_dtype), gated=gated)
+        if feeds_gemm and self.fuse_quant and self.kind == "fp8" and rows <= 64 and w.shape[0] % 8 == 0 and w.shape[0] <= 16384:
+            return self.comm.reduce_quantize_fp8(idx, rows, w.shape[0], self.act_dtype)
         return self.comm.reduce(idx, torch.empty_like(part))
 
     def run(self, x: torch.Tensor) -> torch.Tensor:
@@ -149,7 +158,9 @@ class DecodeStep:
             attn = qkv[:, :a_width]  # stand-in for this rank's attention heads' output
             if attn.data_ptr() % 16 or (attn.stride(0) * attn.element_size()) % 16:
                 attn = attn.contiguous()  # the GEMM takes strided rows as long as they stay 16-byte aligned
-            o = self._row_parallel(attn, *layer.w["o"], nxt_w[(li, "o")])
+            o = self._row_parallel(attn, *layer.w["o"], nxt_w[(li, "o")], feeds_gemm=True)
             gu = self._project(o, *layer.w["gate_up"], nxt_w[(li, "gate_up")])
-            x = self._row_parallel(gu, *layer.w["down"], nxt_w[(li, "down")], gated=True)
+            # the last layer's sum is the step's result; every other one only feeds the next layer's QKV projection
+            x = self._row_parallel(gu, *layer.w["down"], nxt_w[(li, "down")], gated=True,
+                                   feeds_gemm=li + 1 < len(self.layers))
         return x

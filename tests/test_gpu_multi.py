@@ -1,5 +1,6 @@
 """Multi-GPU tests (need >= 2 GPUs on the box; skipped otherwise): the one-shot peer-memory all-reduce against an
-fp32 rank-order sum, and the tensor-parallel decode step with it against the same step over NCCL."""
+fp32 rank-order sum, its fusion with the FP8 quantizer against the two separate kernels (bitwise), and the
+tensor-parallel decode step with it against the same step over NCCL."""
 import os
 import socket
 
@@ -26,7 +27,7 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        ar = CM.OneShotAllReduce(None, dev, max_bytes=32 * 8192 * 2, ctas=16)
+        ar = CM.OneShotAllReduce(None, dev, max_bytes=64 * 8192 * 2, ctas=16)
         res = {}
         for it, (m, dt) in enumerate([(1, torch.bfloat16), (8, torch.bfloat16), (32, torch.bfloat16), (4, torch.float32)]):
             g = torch.Generator(device=dev).manual_seed(100 + rank)
@@ -39,6 +40,25 @@ def _worker(rank, world, port, out_dir):
             for r in range(1, world):
                 want = want + gathered[r].float()          # rank order, fp32, like the kernel
             res[f"ar{it}"] = bool(torch.equal(got, want.to(dt)))
+        # all-reduce fused with the FP8 quantizer == all-reduce, then quantize_fp8, bit for bit
+        res["arq"] = True
+        for it, (m, dt) in enumerate([(1, torch.bfloat16), (8, torch.bfloat16), (32, torch.float16), (64, torch.bfloat16)]):
+            g = torch.Generator(device=dev).manual_seed(200 + 7 * it + rank)
+            part = (torch.randn(m, 8192, device=dev, generator=g) * (0.01 + rank)).to(dt)
+            if m == 8:
+                part[3].zero_()  # an all-zero row takes the min_scale branch
+            for keep in (False, True):
+                idx = 4 * it + 2 * int(keep)  # consecutive all-reduces alternate between the two buffers
+                ar.view(idx, (m, 8192), dt).copy_(part)
+                summed = ar.reduce(idx, torch.empty_like(part))
+                q_ref, s_ref = L.quantize_fp8(summed)
+                ar.view(idx + 1, (m, 8192), dt).copy_(part)
+                out = torch.full_like(part, float("nan")) if keep else None
+                q, sc = ar.reduce_quantize_fp8(idx + 1, m, 8192, dt, out=out)
+                same = torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(sc.flatten(), s_ref.flatten())
+                if keep:
+                    same = same and torch.equal(out, summed)
+                res["arq"] = res["arq"] and bool(same)
         # graph replay: flags return to zero, so the same captured launch works again and again
         part = torch.randn(8, 8192, device=dev, generator=torch.Generator(device=dev).manual_seed(rank)).to(torch.bfloat16)
         buf, out = ar.view(0, (8, 8192), torch.bfloat16), torch.empty(8, 8192, device=dev, dtype=torch.bfloat16)
@@ -67,6 +87,11 @@ def _worker(rank, world, port, out_dir):
         y_nccl = TP.DecodeStep("bf16", 2, world, rank, dev, shape=shape).run(x)
         ar2 = CM.OneShotAllReduce(None, dev, max_bytes=4 * 1024 * 2, ctas=4)
         y_one = TP.DecodeStep("bf16", 2, world, rank, dev, shape=shape, comm=ar2).run(x)
+        # FP8 step: the fused all-reduce + quantizer must not change a single bit of the step's result
+        ar3 = CM.OneShotAllReduce(None, dev, max_bytes=4 * 1024 * 2, ctas=4)
+        y_sep = TP.DecodeStep("fp8", 2, world, rank, dev, shape=shape, comm=ar3, fuse_quant=False).run(x)
+        y_fus = TP.DecodeStep("fp8", 2, world, rank, dev, shape=shape, comm=ar3, fuse_quant=True).run(x)
+        res["fp8_fused_equal"] = bool(torch.equal(y_sep, y_fus)) and bool(torch.isfinite(y_fus.float()).all())
         torch.cuda.synchronize()
         denom = y_nccl.float().abs().max().clamp_min(1e-6)
         res["tp_close"] = float(((y_one.float() - y_nccl.float()).abs().max() / denom).item())
@@ -86,4 +111,5 @@ def test_oneshot_allreduce_and_tp_step(tmp_path):
         res = torch.load(tmp_path / f"r{r}.pt")
         assert all(res[f"ar{i}"] for i in range(4)), res
         assert res["replay"] and res["status"] == 0, res
+        assert res["arq"] and res["fp8_fused_equal"], res
         assert res["tp_close"] < 3e-2, res  # bf16 partials are rounded before NCCL sums them, fp32 here
