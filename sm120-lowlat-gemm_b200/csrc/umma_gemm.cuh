@@ -3,9 +3,11 @@
 // One CTA computes a 128 x BQ output tile for one K partition:
 //   warp 0      TMA producer: 128-byte-swizzled tiles of A and B into a ring of shared-memory stages
 //   warp 1      allocates tensor memory and issues tcgen05.mma (accumulator lives in tensor memory)
-//   warps 2-5   epilogue: tcgen05.ld the accumulator, scale / bias / convert / store, split-K reduction;
-//               for the mixed kinds (W8A16, W4A16) they first widen the weight tile exactly into tensor memory
-//               (the MMA then takes A from tensor memory); for NVFP4 they feed the block scales
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, scale / bias / convert / store, split-K reduction; while it
+//               has nothing to do, one of them asks for the CTA's later weight stages to be brought into L2
+//   warps 6-    helpers, only for some kinds: NVFP4 - four warps put the block scales of every stage into the layout
+//               the MMA's scale copy reads; W8A16 / W4A16 - 8 / 16 warps widen the weight tile exactly into tensor
+//               memory (the MMA then takes A from there), in two groups that take alternate stages
 // The host maps (activation, weight) onto (A, B): with few tokens the weight is A ("swap": its rows fill the 128
 // MMA rows, the tokens sit on the narrow N side and y is stored transposed).
 //

@@ -217,6 +217,30 @@ def test_deep_pipelines(kind):
     no_expired_wait()
 
 
+@pytest.mark.parametrize("kind", ["nvfp4", "w4a16_bf16", "w4a16_f16"])
+def test_block_scales_by_tma_equal_per_thread_copies(kind):
+    """Block scales whose rows are 16-byte aligned travel by TMA, others by per-thread 4-byte copies: the same numbers
+    through both routes (the second time from a buffer shifted by 4 bytes) must give the same bits."""
+    n, k = 300, 5 * 256  # K / 16 = 80 scale bytes per row: a multiple of 16
+    for m, cfg, ksplit in [(3, 0, 1), (16, 5 if kind == "nvfp4" else 0, 1), (40, 2, 2)]:
+        x, w, kw, xd, wd = operands(kind, m, n, k, seed=11 + m)
+        c = TcChoice(cfg=cfg, swap=True, stages=3, ksplit=ksplit)
+        y_tma = L.gemm(x, w, out_dtype=torch.float32, plan=Plan(tc={m: c}), **kw)
+        shifted = dict(kw)
+        for name in ("w_block_scale", "x_block_scale"):
+            if name in kw:
+                t = kw[name]
+                buf = torch.empty(t.numel() + 16, dtype=torch.uint8, device=t.device)
+                view = buf[4:4 + t.numel()].view(t.shape)
+                view.copy_(t.view(torch.uint8))
+                assert view.data_ptr() % 16 == 4
+                shifted[name] = view.view(t.dtype)
+        y_cp = L.gemm(x, w, out_dtype=torch.float32, plan=Plan(tc={m: c}), **shifted)
+        assert torch.equal(y_tma, y_cp), (kind, m, c)
+        assert rel_err(y_tma, xd @ wd.T) < TOL
+    no_expired_wait()
+
+
 @pytest.mark.parametrize("kind", ["bf16", "fp8", "nvfp4", "w4a16_bf16"])
 def test_epilogue_bias_alpha_and_16bit_out(kind):
     m, n, k = 7, 130, 512
