@@ -244,19 +244,36 @@ def run_single(args) -> None:
             w, kw = weights()
             L.gemm(xq[m][0], w, x_scale=xq[m][1], out=y_dev[m], **kw)
 
-    copy_stream = torch.cuda.Stream()
+    copy_stream, in_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    x_in = [x_dev, {m: torch.empty_like(x_dev[m]) for m in TOKENS}]  # two sets: step i+1 arrives while step i computes
+    read_done = [None, None]  # event after the quantizers that read a set
 
-    def e2e_step(_i):  # the call a user makes, from pinned host activations to pinned host results
+    def e2e_step(i):  # the call a user makes, from pinned host activations to pinned host results
         main = torch.cuda.current_stream()
+        xs = x_in[i & 1]
+        if i == 0:
+            read_done[0] = read_done[1] = None  # a new capture (or the eager warm-up) starts: no events carried over
+        if read_done[i & 1] is None:
+            in_stream.wait_stream(main)
+        else:
+            in_stream.wait_event(read_done[i & 1])  # the set's previous contents have been consumed
+        arrived = {}
+        with torch.cuda.stream(in_stream):  # inputs come in on their own stream, ahead of the GEMMs that need them
+            for m in TOKENS:
+                xs[m].copy_(x_host[m], non_blocking=True)
+                arrived[m] = in_stream.record_event()
         for m in TOKENS:
             w, kw = weights()
-            x_dev[m].copy_(x_host[m], non_blocking=True)
-            q, s = L.quantize_fp8(x_dev[m])
+            main.wait_event(arrived[m])
+            q, s = L.quantize_fp8(xs[m])
+            if m == TOKENS[-1]:
+                read_done[i & 1] = main.record_event()
             L.gemm(q, w, x_scale=s, out=y_dev[m], **kw)
             copy_stream.wait_stream(main)          # results leave on a second stream while the next GEMM runs
             with torch.cuda.stream(copy_stream):
                 y_host[m].copy_(y_dev[m], non_blocking=True)
         main.wait_stream(copy_stream)
+        main.wait_stream(in_stream)
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -305,7 +322,7 @@ def run_single(args) -> None:
                    "pct_of_8tbs": 100 * value / 8000.0},
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": sum(m * K_IN * 2 for m in TOKENS),
                 "d2h_bytes_per_step": sum(m * N_OUT * 2 for m in TOKENS), "ms_per_step": ms_e2e / args.steps,
-                "path": "pinned host x -> H2D -> quantize_fp8 -> gemm -> D2H pinned y (copy-out on a second stream), captured in a CUDA graph"},
+                "path": "pinned host x -> H2D (own stream, one step ahead) -> quantize_fp8 -> gemm -> D2H pinned y (copy-out on a second stream), captured in a CUDA graph"},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_source": pk["source"],
@@ -376,6 +393,19 @@ def run_tp(args) -> None:
             step.run(x)
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
+    if comm is not None:
+        # a bounded wait that expired in the library's all-reduce shows in the device status word: then every rank
+        # goes back to NCCL together instead of timing waits
+        from lowlat_gemm import _native as NV
+        bad = torch.tensor([NV.device_status()], device=dev, dtype=torch.int32)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()) != 0:
+            comm, comm_note = None, f"nccl all_reduce (the library's all-reduce reported status {int(bad.item())} in the warm-up)"
+            step = TP.DecodeStep(TP_KIND, layers, world, rank, dev, prefetch_bytes=0, comm=None)
+            with torch.cuda.stream(side):
+                step.run(x)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
     _progress("eager warm-up done")
     step.gemms = step.collectives = 0
     with torch.cuda.stream(side):

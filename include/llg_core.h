@@ -172,7 +172,9 @@ LLG_API int llg_device_status(uint32_t* status);
  * layer. buffers_dev / flags_dev are DEVICE arrays of `world` device pointers (index = rank) to every rank's data
  * buffer and flag words; each rank must have written its partial into buffers_dev[rank] on `stream` (or before)
  * and must use a different data buffer for consecutive calls (two alternating buffers are enough). The flag words
- * (ctas * world uint32 per rank) must be zero before the first call and are zero again after every call. Partials
+ * (2 * LLG_AR_MAX_CTAS * world uint32 per rank: arrival counters that the peers add to, then this rank's count of
+ * consumed signals) must be zero before the first call and belong to the library afterwards: counters only grow, so a
+ * captured launch replays, provided every rank issues the same sequence of all-reduce calls. Partials
  * are added in rank order in fp32, so all ranks get identical bits. bytes must be a multiple of 16, buffers 16-byte
  * aligned, world <= 8, 1 <= ctas <= LLG_AR_MAX_CTAS. Waits are bounded (~1 s): on expiry the device status word
  * is set (llg_device_status) and the result is undefined, but nothing hangs.
@@ -184,7 +186,7 @@ LLG_API int llg_allreduce_oneshot(const void* const* buffers_dev, uint32_t* cons
 /* The same all-reduce followed, in the same kernel, by the per-token FP8 activation quantizer
  * (lowlat_gemm/__init__.py:quantize_fp8, csrc/quant.cu:43-66 of the reference): the partials are [rows, cols] 16-bit
  * values, contiguous, at the start of every rank's buffer; one CTA and one flag set per row, so rows <= LLG_AR_MAX_CTAS
- * and the flag words must hold rows * world entries; cols a multiple of 8, at most LLG_ARQ_MAX_COLS. Writes
+ * (same flag words as above); cols a multiple of 8, at most LLG_ARQ_MAX_COLS. Writes
  * q [rows, ldq] (e4m3 bytes) and scale_out [rows] = max(amax / 448, min_scale), bit-identical to quantize_fp8 applied
  * to the all-reduce's 16-bit result, and that result itself to `out` unless out is NULL. Same buffer alternation,
  * flag and bounded-wait rules as llg_allreduce_oneshot. No counterpart in the reference. */

@@ -5,11 +5,16 @@
 // symmetric buffer (peer-mapped memory); each rank then reads all partials with plain 16-byte peer loads and adds them
 // in rank order in fp32, so every rank obtains the same bits, run after run. No multicast, no TMA, no NVLS.
 //
-// Synchronisation: each CTA exchanges one flag with the same CTA on every peer (compare-and-swap 0 -> 1 to signal,
-// 1 -> 0 to consume, so flags are back at zero afterwards and the kernel can be replayed from a CUDA graph). Every
-// spin is bounded; on expiry the kernel records a status code and carries on without waiting (the result is then
-// undefined, the device stays usable). Buffers must alternate between consecutive all-reduces (the caller uses two):
-// a rank may still be reading a peer's buffer of all-reduce n while that peer already writes the buffer of n+1.
+// Synchronisation: each CTA (or row) exchanges one signal with the same CTA on every peer. A signal is a system-scope
+// add of 1 to a counter in the peer's memory, sent after a system-scope fence and without waiting for a reply; the
+// receiver keeps, in its own memory, how many signals it has consumed from each peer and spins until the counter has
+// passed that number. Counters only grow (compared through their wrapped difference), nothing is reset, so a captured
+// launch replays as often as wanted as long as every rank replays the same sequence. Every spin is bounded; on
+// expiry the kernel records a status code and carries on without waiting (the result is then undefined, the device
+// stays usable). Buffers must alternate between consecutive all-reduces (the caller uses two): a rank may still be
+// reading a peer's buffer of all-reduce n while that peer already writes the buffer of n+1.
+// Flag memory per rank: 2 * slots * world words, zero before the first call - [slot][peer] arrival counters, written
+// by the peers, then [slot][peer] consumed counts, private to the rank.
 //
 // The reference has no collective of any kind; this stands where NCCL's all_reduce would be called.
 #include <cuda_bf16.h>
@@ -24,17 +29,29 @@ namespace {
 constexpr int kArThreads = 256;
 constexpr long long kArSpinCycles = 2000000000ll;  // ~1 s
 
-__device__ __forceinline__ bool flag_send(uint32_t* slot) {
-  const long long t0 = clock64();
-  while (atomicCAS_system(slot, 0u, 1u) != 0u)
-    if (clock64() - t0 > kArSpinCycles) return false;
-  return true;
+__device__ __forceinline__ void flag_send(uint32_t* counter) {
+  atomicAdd_system(counter, 1u);  // result unused: a reduction, nothing comes back over the link
 }
-__device__ __forceinline__ bool flag_recv(uint32_t* slot) {
+// Waits until `counter` (written by one peer) has passed this rank's count of consumed signals, which it advances.
+__device__ __forceinline__ bool flag_recv(const uint32_t* counter, uint32_t* consumed) {
+  const uint32_t want = *consumed + 1u;
+  *consumed = want;
   const long long t0 = clock64();
-  while (atomicCAS_system(slot, 1u, 0u) != 1u)
+  for (;;) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if ((int32_t)(seen - want) >= 0) return true;
     if (clock64() - t0 > kArSpinCycles) return false;
-  return true;
+  }
+}
+// One signal to and one from peer `peer`, for slot `slot` (a CTA or a row) of `slots`.
+__device__ __forceinline__ bool exchange(uint32_t* const* flags, int slot, int slots, int peer, int rank, int world) {
+  __threadfence_system();
+  flag_send(flags[peer] + (int64_t)slot * world + rank);
+  uint32_t* const mine = flags[rank];
+  const bool ok = flag_recv(mine + (int64_t)slot * world + peer, mine + ((int64_t)slots + slot) * world + peer);
+  __threadfence_system();
+  return ok;
 }
 
 struct ArDev {
@@ -80,11 +97,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_oneshot_kernel(const ArD
   if (tid == 0) failed = 0;
   __syncthreads();
   if (tid < p.world) {
-    __threadfence_system();
-    bool ok = flag_send(p.flags[tid] + (int64_t)cta * p.world + p.rank);      // tell peer `tid`
-    ok = flag_recv(p.flags[p.rank] + (int64_t)cta * p.world + tid) && ok;     // hear from peer `tid`
-    __threadfence_system();
-    if (!ok) {
+    if (!exchange(p.flags, cta, LLG_AR_MAX_CTAS, tid, p.rank, p.world)) {  // tell peer `tid`, hear from peer `tid`
       failed = 1;
       atomicCAS(p.status, 0u, 16u);
     }
@@ -147,11 +160,7 @@ __global__ void __launch_bounds__(kArqThreads) allreduce_quant_fp8_kernel(const 
   pdl_wait();
   __shared__ float red[kArqThreads / 32];
   if (tid < p.world) {
-    __threadfence_system();
-    bool ok = flag_send(p.flags[tid] + (int64_t)row * p.world + p.rank);
-    ok = flag_recv(p.flags[p.rank] + (int64_t)row * p.world + tid) && ok;
-    __threadfence_system();
-    if (!ok) atomicCAS(p.status, 0u, 16u);
+    if (!exchange(p.flags, row, LLG_AR_MAX_CTAS, tid, p.rank, p.world)) atomicCAS(p.status, 0u, 16u);
   }
   __syncthreads();
   const int units = p.cols >> 3;  // 8 values = 16 bytes per unit

@@ -1,7 +1,7 @@
 """One-shot all-reduce over peer-mapped ("symmetric") memory for the row-parallel boundaries of a tensor-parallel
 decode layer: the GEMM writes its partial straight into this rank's symmetric buffer, one small kernel
 (`llg_allreduce_oneshot`) then reads every rank's partial over NVLink and adds them in rank order. Plain peer loads and
-compare-and-swap flags only - no multicast, no NVLS. The reference has nothing comparable (no multi-GPU code); the
+one-way counter signals only - no multicast, no NVLS. The reference has nothing comparable (no multi-GPU code); the
 baseline this replaces is `torch.distributed.all_reduce` (NCCL).
 
 torch is used for what it is here for: allocating and exchanging the peer mappings
@@ -32,7 +32,10 @@ class OneShotAllReduce:
             raise ValueError("one-shot all-reduce supports at most 8 ranks")
         self.device, self.ctas, self.max_bytes = device, ctas, (max_bytes + 15) // 16 * 16
         self.bufs = [symm.empty(self.max_bytes, dtype=torch.uint8, device=device) for _ in range(buffers)]
-        self.flags = symm.empty(max(ctas, N.AR_MAX_CTAS) * self.world, dtype=torch.int32, device=device)
+        if ctas > N.AR_MAX_CTAS:
+            raise ValueError(f"at most {N.AR_MAX_CTAS} CTAs per all-reduce")
+        # per rank: [AR_MAX_CTAS][world] arrival counters (the peers add to them) + as many consumed counts (private)
+        self.flags = symm.empty(2 * N.AR_MAX_CTAS * self.world, dtype=torch.int32, device=device)
         self.flags.zero_()
         handles = [symm.rendezvous(b, self.group) for b in self.bufs]
         fh = symm.rendezvous(self.flags, self.group)

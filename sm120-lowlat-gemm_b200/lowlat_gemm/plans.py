@@ -199,13 +199,15 @@ _WBITS = {"bf16": 16, "f16": 16, "fp8": 8, "int8": 8, "nvfp4": 4, "w8a16_bf16": 
 
 
 def default_tc_choice(kind: str, m: int, n: int, k: int, sm_count: int) -> TcChoice:
-    """Weight on the 128-row side ("swap") while the token count fits one narrow tile, activations there otherwise.
-    The kernel is persistent (one CTA per SM walks the (tile, K partition) items), so the K split is picked with a small
-    cost model: weight bytes over the fraction of SMs kept busy by the last round, plus the split-K partial traffic,
-    plus a fixed cost per item."""
+    """Weight on the 128-row side ("swap") while the token count fits one narrow tile, activations there otherwise;
+    two K atoms per stage where they fit (fewer barrier round trips per byte). The K split is picked with a small cost
+    model: weight bytes over the fraction of SMs kept busy by the last round, plus the split-K partial traffic, plus a
+    fixed cost per round and per stage of the chain one CTA walks; splits up to 8 reduce over the cluster. Without a split, kinds that stream (everything but
+    the mixed ones) take three stages when three fit 110 KB: two CTAs then fit an SM, so the next kernel of a dependent
+    chain is resident early (what the tuner finds on B200 for every baseline shape)."""
     swap = kind in _MIXED or m <= 64
     if swap:
-        cfg = 0 if m <= 16 else 1 if m <= 32 else 2 if m <= 64 else 3 if m <= 128 else 4
+        cfg = 5 if m <= 16 else 6 if m <= 32 else 7 if m <= 64 else 3 if m <= 128 else 4
     else:
         cfg = 4 if n >= 2048 and m >= 256 else 3
     cfg = _fit_cfg(kind, cfg)
@@ -215,18 +217,34 @@ def default_tc_choice(kind: str, m: int, n: int, k: int, sm_count: int) -> TcCho
     nk = -(-k // (KINDS[kind][1] * cfg_atoms(cfg)))
     weight = n * k * _WBITS[kind] / 8
     best, best_t = 1, None
-    for ks in range(1, 17):
+    for ks in range(1, 9):  # up to what a cluster can reduce
         if ks > 1 and nk // ks < 2:
             break
         items = tiles * ks
         rounds = -(-items // sm_count)
         busy = items / (rounds * sm_count)
+        if ks == 1 and swap:
+            # without a split the launcher shortens the row pitch (down to 32 rows) so that the tiles fill whole rounds
+            tq = -(-q // bq)
+            want = -(-tiles // sm_count) * sm_count // tq
+            pitch = min(bp, max(32, -(-p // max(want, 1))))
+            items = -(-p // pitch) * tq
+            rounds = -(-items // sm_count)
+            busy = items / (rounds * sm_count)
         partials = 2.0 * ks * p * q * 4 if ks > 1 else 0.0
-        t = (weight / busy + 0.5 * partials) / 6.5e6 + rounds * 0.4  # microseconds
+        # microseconds: streaming, a fixed cost per round, and the serial chain of stages one CTA walks per item
+        t = (weight / busy + 0.5 * partials) / 6.5e6 + rounds * 0.4 + (nk / ks) * 0.12
         if best_t is None or t < best_t - 1e-9:
             best, best_t = ks, t
-    stages = max(2, min(max_stages(kind, cfg), nk + 1))
-    return TcChoice(cfg=cfg, swap=swap, stages=stages, ksplit=best)
+    top = max_stages(kind, cfg)
+    if best == 1 and kind not in _MIXED and 3 * stage <= 110 * 1024:
+        stages = 3
+    elif kind in _MIXED:
+        stages = min(top, 4)
+    else:
+        stages = top
+    stages = max(2, min(stages, top, nk + 1))
+    return TcChoice(cfg=cfg, swap=swap, stages=stages, ksplit=best, cluster=best > 1)
 
 
 def default_plan(kind: str, n: int, k: int, sm_count: int) -> Plan:
