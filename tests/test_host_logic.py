@@ -126,6 +126,17 @@ def test_heuristics_fill_the_gpu():
         p, q = (n, m) if c.swap else (m, n)
         ctas = -(-p // bp) * -(-q // bq) * c.ksplit
         assert ctas >= sms // 2 or kind == "int8"
+    # what the tuner finds on B200 for the baseline shapes: two K atoms per stage for decode batches; the streaming
+    # kinds unsplit with three stages where the row pitch can spread the tiles; small weights split over a cluster
+    c = L.default_tc_choice("fp8", 16, 14336, 4096, sms)
+    assert (c.cfg, c.stages, c.ksplit, c.cluster) == (5, 3, 1, False)
+    c = L.default_tc_choice("nvfp4", 8, 28672, 8192, sms)
+    assert c.cfg == 5 and c.ksplit == 1 and c.stages == L.max_stages("nvfp4", 5)
+    c = L.default_tc_choice("int8", 8, 4096, 4096, sms)
+    assert c.cfg == 5 and 2 <= c.ksplit <= 8 and c.cluster
+    assert L.default_tc_choice("w4a16_bf16", 4, 28672, 8192, sms).cfg == 0  # two atoms do not fit for W4A16
+    for m in (1, 16, 64, 256):
+        assert L.default_tc_choice("fp8", m, 1280, 8192, sms).ksplit <= 8
     o = L.default_skinny_order(11008, 4096, sms)
     assert o.lanes_per_row == 32 and 1 <= o.ksplit <= 16
     plan = L.default_plan("bf16", 11008, 4096, sms)
