@@ -93,6 +93,7 @@ class DecodeStep:
         self._g4_host = float(nvfp4_global)  # host copy: nothing on the launch path may read the device
         self.collectives = 0
         self.gemms = 0
+        self.quants = 0
         self.comm = comm if tp > 1 else None  # a comm.OneShotAllReduce, or None for NCCL all_reduce
         self._ar_index = 0
         self.fuse_quant = fuse_quant  # FP8 with `comm`: all-reduce and the next activation quantizer as one kernel
@@ -116,6 +117,8 @@ class DecodeStep:
         if gated and self._api is None:  # host stand-in used by the CPU tests
             half = h.shape[1] // 2
             h, gated = torch.nn.functional.silu(h[:, :half]) * h[:, half:], False
+        if self.kind in ("fp8", "nvfp4") or gated:
+            self.quants += 1  # one quantizer / activation kernel of the library
         if self.kind == "fp8":
             q, s = self._api.silu_mul_quantize_fp8(h) if gated else self._q8(h)
             return self._gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
