@@ -65,7 +65,10 @@ enum { LLG_QUANT_FP8_STATIC = 0, LLG_QUANT_FP8_PER_TOKEN = 1, LLG_QUANT_INT8_PER
  * Skinny streaming GEMV: y[M,N] = x[M,K] @ w[N,K]^T for bf16/f16 with M <= 16, fp32 accumulation in an order that
  * depends on (K, lanes_per_row, ksplit) only, so a row of the result is bit-identical for every M and tile.
  * Stands in for torch.ops.lowlat_gemm.skinny_out (reference csrc/ops.cpp:59-129, 381-385; launch descriptor
- * csrc/params.h:10-34; kernel csrc/gemv.cuh:74-234). */
+ * csrc/params.h:10-34; kernel csrc/gemv.cuh:74-234, whose summation order csrc/gemv.cuh:6-12 is kept bit for bit).
+ * The kernel is a persistent one-wave grid: each CTA owns a contiguous range of rows. rows / unroll / warps are tile
+ * knobs with the reference's ranges; here they set the row groups a warp carries (rows), the K depth of a pipeline
+ * stage (unroll) and the compute warps per CTA (2 * warps). */
 typedef struct llg_skinny_args {
   const void* x;  int64_t ldx;   /* [M,K], row stride in elements, 16-byte aligned, ldx % 8 == 0 */
   const void* w;  int64_t ldw;   /* [N,K], same element type as x */
@@ -76,11 +79,16 @@ typedef struct llg_skinny_args {
   int32_t rows, unroll, lanes_per_row, warps, ksplit; /* tile: (rows,unroll) in {(1,2),(1,4),(1,8),(2,2),(2,4),(4,2)} */
   int32_t cluster;               /* split-K reduced through cluster shared memory (ksplit <= 8) */
   float* ws;      int64_t ws_elems;        /* split-K partials, >= ksplit*M*N floats (workspace mode) */
-  int32_t* counters; int64_t counters_elems; /* >= ceil(N / rows_per_block) ints, zero between launches */
+  int32_t* counters; int64_t counters_elems; /* workspace mode: one per row range, zero between launches; at least 1,
+                                                llg_skinny_ranges(N, ksplit) for full speed */
   const void* prefetch; int64_t prefetch_bytes; /* optional L2 prefetch range (16-byte aligned), NULL = none */
 } llg_skinny_args;
 
 LLG_API int llg_skinny(const llg_skinny_args* args, void* stream);
+
+/* Row ranges (= CTAs along N, = split-K counters) llg_skinny uses on the current device for this N and ksplit when
+ * enough counters are passed. No counterpart in the reference, whose grid follows from the tile. */
+LLG_API int32_t llg_skinny_ranges(int32_t N, int32_t ksplit);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * Tensor-core GEMM (tcgen05): C[p,q] = sum_k A[p,k] B[q,k], then

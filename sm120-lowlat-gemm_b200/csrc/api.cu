@@ -246,6 +246,13 @@ int llg_tc_info(int32_t kind, int32_t cfg, int32_t out[4]) {
 
 // ---------------------------------------------------------------------------------------------------------------
 
+int32_t llg_skinny_ranges(int32_t N, int32_t ksplit) {
+  if (N < 1 || ksplit < 1) return 0;
+  int64_t gx = sm_count() / ksplit;
+  if (gx < 1) gx = 1;
+  return (int32_t)(gx < N ? gx : N);
+}
+
 int llg_skinny(const llg_skinny_args* a, void* stream) {
   if (!a) return fail(LLG_E_INVALID, "null arguments");
   const int ru = a->rows * 16 + a->unroll;
@@ -262,17 +269,16 @@ int llg_skinny(const llg_skinny_args* a, void* stream) {
   if (a->N < 1) return fail(LLG_E_INVALID, "N or K too large");
   if (a->ldx % 8 || a->ldw % 8) return fail(LLG_E_INVALID, "x and w row strides must be multiples of 8 elements");
   if (!aligned(a->x, 16) || !aligned(a->w, 16)) return fail(LLG_E_INVALID, "x and w must be 16-byte aligned");
-  const int64_t rows_cta = (int64_t)a->warps * (32 / a->lanes_per_row) * a->rows;
-  const int64_t columns = (a->N + rows_cta - 1) / rows_cta;
   const bool cluster = a->cluster && a->ksplit > 1;
   if (cluster && a->ksplit > 8) return fail(LLG_E_INVALID, "cluster split-K supports ksplit <= 8, got %d", a->ksplit);
-  if (a->ksplit > 1 && !cluster) {
+  const bool use_ws = a->ksplit > 1 && !cluster;
+  if (use_ws) {
     if (!a->ws || !a->counters) return fail(LLG_E_INVALID, "workspace must be contiguous float32, counters contiguous int32");
     if (a->ws_elems < (int64_t)a->ksplit * a->M * a->N)
       return fail(LLG_E_INVALID, "workspace has %lld floats, needs %lld", (long long)a->ws_elems,
                   (long long)a->ksplit * a->M * a->N);
-    if (a->counters_elems < columns)
-      return fail(LLG_E_INVALID, "counters has %lld, needs %lld", (long long)a->counters_elems, (long long)columns);
+    // one counter per row range; with fewer counters than llg_skinny_ranges() the launch uses fewer, longer ranges
+    if (a->counters_elems < 1) return fail(LLG_E_INVALID, "counters has %lld, needs at least 1", (long long)a->counters_elems);
   }
   if (a->prefetch && !aligned(a->prefetch, 16))
     return fail(LLG_E_INVALID, "prefetch tensor must be contiguous and 16-byte aligned");
@@ -281,11 +287,14 @@ int llg_skinny(const llg_skinny_args* a, void* stream) {
   p.x = a->x; p.w = a->w; p.y = a->y;
   p.ldx = a->ldx; p.ldw = a->ldw; p.ldy = a->ldy;
   p.M = a->M; p.N = a->N; p.K = a->K; p.ksplit = a->ksplit;
-  p.ws = a->ksplit > 1 && !cluster ? a->ws : nullptr;
-  p.counters = a->ksplit > 1 && !cluster ? reinterpret_cast<unsigned*>(a->counters) : nullptr;
+  p.ws = use_ws ? a->ws : nullptr;
+  p.counters = use_ws ? reinterpret_cast<unsigned*>(a->counters) : nullptr;
+  p.max_ranges = use_ws ? (int)(a->counters_elems < INT32_MAX ? a->counters_elems : INT32_MAX) : INT32_MAX;
   p.pf = a->prefetch; p.pf_bytes = a->prefetch ? a->prefetch_bytes : 0;
   p.out_fp32 = a->out_fp32 != 0;
   p.cluster = cluster;
+  p.status = status_word_device_ptr();
+  if (!p.status) return fail(LLG_E_CUDA, "no device status word");
   const bool pdl = pdl_on();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
@@ -296,7 +305,9 @@ int llg_skinny(const llg_skinny_args* a, void* stream) {
   }
   if (e != cudaSuccess) {
     cudaGetLastError();
-    return fail(LLG_E_CUDA, "skinny: no kernel for M=%d rows=%d unroll=%d (%s)", a->M, a->rows, a->unroll, cudaGetErrorString(e));
+    return fail(e == cudaErrorInvalidConfiguration ? LLG_E_CONFIG : LLG_E_CUDA,
+                "skinny: cannot launch M=%d N=%d K=%d rows=%d unroll=%d warps=%d (%s)", a->M, a->N, a->K, a->rows, a->unroll,
+                a->warps, cudaGetErrorString(e));
   }
   return LLG_OK;
 }

@@ -18,6 +18,10 @@ enum : uint32_t {
   ST_EPILOGUE_WAIT = 3,        // epilogue waited for the accumulator
   ST_CONVERT_WAIT = 4,         // converter / scale warps waited for a buffer
   ST_DRAIN_WAIT = 5,           // producer waited for its own copies while leaving early
+  ST_SKINNY_PRODUCER_WAIT = 6, // skinny GEMV: weight producer waited for a free stage
+  ST_SKINNY_CONVERT_WAIT = 7,  // skinny GEMV: activation converters waited for a free stage
+  ST_SKINNY_COMPUTE_WAIT = 8,  // skinny GEMV: compute warps waited for a full stage
+  ST_ALLREDUCE_WAIT = 16,      // all-reduce: a peer's signal did not arrive
 };
 unsigned int* status_word_device_ptr();  // device address of the status word of the current device (cached)
 
@@ -59,15 +63,24 @@ struct SkinnyDev {
   const void* x;
   const void* w;
   void* y;
-  int64_t ldx, ldw, ldy;
+  int64_t ldx, ldw, ldy;  // elements
   int M, N, K, ksplit;
   float* ws;
   unsigned* counters;
+  int max_ranges;         // workspace split-K: counters available, one per row range (= gridDim.x)
   const void* pf;
   int64_t pf_bytes;
-  unsigned char out_fp32, cluster, pdl_early;
+  unsigned* status;
+  // geometry, filled in by the launcher
+  int rounds;             // rounds of LPR vectors per pipeline stage
+  int stages;             // ring depth
+  int rows_pass;          // rows one pass over K covers
+  int pitch;              // bytes between the rows of a weight stage
+  int xslot_off;          // offset of the converted activations inside a stage
+  int stage_bytes;
+  unsigned char out_fp32, cluster;
 };
-// One translation unit per lanes-per-row; returns cudaErrorInvalidValue for an unsupported tile.
+// One translation unit per lanes-per-row. rows / unroll / warps are tile knobs that never change a result bit.
 cudaError_t skinny_launch_l8(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
 cudaError_t skinny_launch_l16(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
 cudaError_t skinny_launch_l32(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);

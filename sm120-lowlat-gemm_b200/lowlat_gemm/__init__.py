@@ -21,7 +21,7 @@ from .api import (_FP4_KINDS, _workspace, _ws, gemm, kind_of, pdl_enabled, quant
 from .plans import (KINDS, MAX_STAGES, NUM_CFGS, SKINNY_MAX_TOKENS, _MIXED, Plan, SkinnyOrder, SkinnyTile,  # noqa: F401
                     TcChoice, _file_key, _nearest, _packaged_path, _tc_lookup, cfg_atoms, default_plan,
                     default_skinny_order, default_tc_choice, get_plan, load_plans, max_stages, prefer_lowlat,
-                    save_plans, set_plan, smem_budget, tc_info)
+                    save_plans, set_plan, skinny_ranges, smem_budget, tc_info)
 
 __all__ = [
     "KINDS", "Plan", "SkinnyOrder", "SkinnyTile", "TcChoice", "default_plan", "gemm", "get_plan", "kind_of",

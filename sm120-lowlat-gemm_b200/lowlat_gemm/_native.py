@@ -56,6 +56,7 @@ class GatedQuantArgs(C.Structure):
 # every symbol include/llg_core.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "llg_skinny": (c_i32, [C.POINTER(SkinnyArgs), c_ptr]),
+    "llg_skinny_ranges": (c_i32, [c_i32, c_i32]),
     "llg_tc_gemm": (c_i32, [C.POINTER(TcArgs), c_ptr]),
     "llg_tc_info": (c_i32, [c_i32, c_i32, C.POINTER(c_i32 * 4)]),
     "llg_smem_budget": (c_i32, []),

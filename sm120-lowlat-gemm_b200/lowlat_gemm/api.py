@@ -14,7 +14,7 @@ import torch
 
 from . import _ops  # noqa: F401  (registers torch.ops.lowlat_gemm)
 from .plans import (KINDS, SKINNY_MAX_TOKENS, _MIXED, Plan, _dev, _sm_count, _tc_lookup, default_tc_choice, get_plan,
-                    tc_info)
+                    skinny_ranges, tc_info)
 
 _FP4 = getattr(torch, "float4_e2m1fn_x2", None)
 _FP8 = torch.float8_e4m3fn
@@ -109,9 +109,8 @@ def workspace_need(kind: str, n: int, k: int, max_m: int, device: torch.device |
         if plan.skinny is not None and m <= min(plan.skinny_max_m, SKINNY_MAX_TOKENS):
             o = plan.skinny
             if o.ksplit > 1 and not o.cluster:
-                t = o.tile(m)
                 elems = max(elems, o.ksplit * m * n)
-                counters = max(counters, -(-n // (t.warps * (32 // o.lanes_per_row) * t.rows)))
+                counters = max(counters, skinny_ranges(n, o.ksplit, _sm_count(device)))
             continue
         c = _tc_lookup(plan.tc, m) or default_tc_choice(kind, m, n, k, _sm_count(device))
         if c.ksplit > 1 and not c.cluster:
@@ -166,8 +165,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, *, x_scale=None, w_scale=None, x_bloc
         order = plan.skinny
         tile = order.tile(m)
         if order.ksplit > 1 and not order.cluster:
-            rows_cta = tile.warps * (32 // order.lanes_per_row) * tile.rows
-            ws, cnt = _workspace(device, order.ksplit * m * n, -(-n // rows_cta))
+            ws, cnt = _workspace(device, order.ksplit * m * n, skinny_ranges(n, order.ksplit, _sm_count(device)))
         else:
             ws, cnt = _workspace(device, 0, 0)
         torch.ops.lowlat_gemm.skinny_out(y2, x2, w, ws, cnt, tile.rows, tile.unroll, order.lanes_per_row, tile.warps,

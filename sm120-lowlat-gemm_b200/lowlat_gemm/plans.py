@@ -174,16 +174,26 @@ def cfg_atoms(cfg: int) -> int:
     return 1 + cfg // 5
 
 
+def skinny_ranges(n: int, ksplit: int, sm_count: int) -> int:
+    """Row ranges (CTAs along N, and split-K counters) of a skinny launch: one wave of CTAs, never more than rows."""
+    return max(1, min(n, max(1, sm_count // ksplit)))
+
+
 def default_skinny_order(n: int, k: int, sm_count: int) -> SkinnyOrder:
+    """Summation order and tile for the persistent skinny kernel when nothing was tuned. 16 virtual lanes per row keep
+    the activation reads of a warp inside one shared-memory wavefront; K is split while a CTA would otherwise own
+    fewer than 16 rows (a row range that short does not keep a whole CTA's warps busy) and the splits stay long
+    enough to amortise a pipeline stage. The tile lets one pass over K cover the CTA's whole row range."""
     kv = k // 8
-    lanes = next((c for c in (32, 16, 8) if kv >= 4 * c), 8)
-    rows = 2 if n >= 8192 else 1
-    groups = -(-n // rows)
+    lanes = 16 if kv >= 32 else 8
     ksplit = 1
-    # enough lane groups for ~8 resident warps' worth per SM, but never fewer than two vectors per lane and split
-    while groups * ksplit < 8 * sm_count and kv // (2 * ksplit) >= 2 * lanes and ksplit < 16:
+    while n * ksplit < 16 * sm_count and kv // (2 * ksplit) >= 4 * lanes and ksplit < 8:
         ksplit *= 2
-    return SkinnyOrder(lanes_per_row=lanes, ksplit=ksplit, default_tile=SkinnyTile(rows=rows, unroll=4, warps=4))
+    per_cta = -(-n // skinny_ranges(n, ksplit, sm_count))
+    side_by_side = 16 * (64 // lanes)  # rows of one row group across 16 compute warps
+    rows = 1 if per_cta <= side_by_side else 2 if per_cta <= 2 * side_by_side else 4
+    return SkinnyOrder(lanes_per_row=lanes, ksplit=ksplit, cluster=ksplit > 1,
+                       default_tile=SkinnyTile(rows=rows, unroll=4 if rows < 4 else 2, warps=8))
 
 
 def _fit_cfg(kind: str, cfg: int) -> int:
