@@ -117,6 +117,21 @@ bool make_sf_map(CUtensorMap* m, const void* ptr, int64_t row_bytes, int64_t row
 
 }  // namespace
 
+bool make_dense_map(CUtensorMap* m, const void* ptr, int64_t row_bytes, int64_t rows, int64_t ld_bytes, int box_bytes,
+                    int box_rows, bool streamed) {
+  auto fn = encode_fn();
+  if (!fn || box_bytes % 16 || box_bytes > 1024 || box_rows < 1 || box_rows > 256) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 4), (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 4), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        streamed ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool pdl_on() { return g_pdl.load(std::memory_order_relaxed); }
 
 int sm_count() {
@@ -248,7 +263,7 @@ int llg_tc_info(int32_t kind, int32_t cfg, int32_t out[4]) {
 
 int32_t llg_skinny_ranges(int32_t N, int32_t ksplit) {
   if (N < 1 || ksplit < 1) return 0;
-  int64_t gx = sm_count() / ksplit;
+  int64_t gx = 2 * (int64_t)sm_count() / ksplit;  // small CTAs run two to an SM
   if (gx < 1) gx = 1;
   return (int32_t)(gx < N ? gx : N);
 }

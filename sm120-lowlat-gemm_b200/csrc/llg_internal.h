@@ -18,8 +18,8 @@ enum : uint32_t {
   ST_EPILOGUE_WAIT = 3,        // epilogue waited for the accumulator
   ST_CONVERT_WAIT = 4,         // converter / scale warps waited for a buffer
   ST_DRAIN_WAIT = 5,           // producer waited for its own copies while leaving early
-  ST_SKINNY_PRODUCER_WAIT = 6, // skinny GEMV: weight producer waited for a free stage
-  ST_SKINNY_CONVERT_WAIT = 7,  // skinny GEMV: activation converters waited for a free stage
+  ST_SKINNY_PRODUCER_WAIT = 6, // skinny GEMV: producer waited for a free stage
+  ST_SKINNY_CONVERT_WAIT = 7,  // skinny GEMV: activation converters waited for a stage to land
   ST_SKINNY_COMPUTE_WAIT = 8,  // skinny GEMV: compute warps waited for a full stage
   ST_ALLREDUCE_WAIT = 16,      // all-reduce: a peer's signal did not arrive
 };
@@ -58,6 +58,11 @@ inline cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Tiled map over a row-major byte matrix seen as four-byte elements: box = box_bytes x box_rows, no swizzle (rows of a
+// box are dense in shared memory), zero fill outside the tensor. row_bytes, ld_bytes and box_bytes are multiples of 16.
+bool make_dense_map(CUtensorMap* m, const void* ptr, int64_t row_bytes, int64_t rows, int64_t ld_bytes, int box_bytes,
+                    int box_rows, bool streamed);
+
 // ---- skinny GEMV -------------------------------------------------------------------------------------------------
 struct SkinnyDev {
   const void* x;
@@ -76,8 +81,11 @@ struct SkinnyDev {
   int stages;             // ring depth
   int rows_pass;          // rows one pass over K covers
   int pitch;              // bytes between the rows of a weight stage
-  int xslot_off;          // offset of the converted activations inside a stage
+  int xraw_off;           // offset of the activation box inside a stage
+  int xraw_pitch;         // bytes between its token rows
+  int xslot_off;          // offset of the activations widened to fp32 inside a stage
   int stage_bytes;
+  int w_box_bytes, x_box_bytes;  // bytes the two TMA boxes of a stage deliver
   unsigned char out_fp32, cluster;
 };
 // One translation unit per lanes-per-row. rows / unroll / warps are tile knobs that never change a result bit.

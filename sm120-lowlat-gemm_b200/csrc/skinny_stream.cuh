@@ -13,20 +13,26 @@
 //   * Persistent, one wave: blockIdx.x owns a contiguous range of about N / gridDim.x rows, so every SM streams the
 //     same number of weight bytes; blockIdx.y is the K split.
 //   * Weights never pass through registers on their way in: a producer warp brings one K chunk of every row of the
-//     range into a ring of shared-memory stages with non-multicast bulk copies (cp.async.bulk, one per row and
-//     stage), completion counted on an mbarrier. It starts before the programmatic-dependent-launch wait - weights do
-//     not depend on the previous kernel - so the ring is full when the activations become readable.
-//   * Activations are staged once per stage, not once per lane and token: two converter warps read the stage's slice of
-//     x, widen it to fp32 and store it in the stage in the order the compute warps consume it.
+//     range into a ring of shared-memory stages with ONE tiled TMA load per stage (a box of rows x chunk bytes, no
+//     swizzle, no multicast), completion counted on an mbarrier. Per-row bulk copies were measured first: about 50 ns
+//     per request and SM, which capped the kernel at 3 TB/s. The producer starts before the programmatic-dependent-
+//     launch wait - weights do not depend on the previous kernel - so the ring is full when the activations become
+//     readable.
+//   * Activations come through the same ring, not once per lane and token from global memory: a second TMA box per
+//     stage (tokens x chunk bytes), issued after the dependency wait. Two converter warps widen it to fp32 inside
+//     shared memory, once per stage and CTA, in the order the compute warps read it, so a compute thread spends one
+//     16-byte shared load per two packed multiply-adds of each row it carries and no conversion instruction on x.
+//     (Widening x in registers instead was measured: the conversions are repeated by every thread and by the rows a
+//     warp holds side by side, and from 4 tokens on they, not memory, set the time.)
 //   * A thread owns TWO virtual lanes of a row, p and p + LPR/2 - the partners of the butterfly's first level - and
 //     advances both sums with one packed fma.rn.f32x2 (each half is an IEEE fused multiply-add, so the bits are
 //     those of two scalar fmaf). The LPR/2 threads of a row are lanes of one warp: the first butterfly level is an
 //     add inside the thread, the others are shuffles; no shared memory and no barrier between warps is needed to finish
-//     a row. A warp works on 64/LPR rows side by side and on up to R such row groups.
-//   * Lanes that share a vector pair read the same 16 bytes of activations (a broadcast), lanes of a row read
-//     contiguous weights: both conflict-free.
-//   * Vectors past the end of the split are neutralised exactly: their activations are stored as +0 and their weights
-//     replaced by -0, and fma(-0, +0, s) returns s for every s.
+//     a row. A warp works on 64/LPR rows side by side and on up to R such row groups, which share the widened
+//     activations.
+//   * Lanes of a row read contiguous weights and contiguous activations: conflict-free.
+//   * Vectors past the end of the split are neutralised exactly: their activations are replaced by +0 and their
+//     weights by -0, and fma(-0, +0, s) returns s for every s.
 //   * Every wait is bounded; on expiry the role records a status code, raises the CTA's abort word and all roles
 //     drain.
 #pragma once
@@ -41,24 +47,25 @@
 
 namespace llg {
 
-constexpr int kSkProducerWarps = 1;
 constexpr int kSkConverterWarps = 2;
-constexpr int kSkHelperWarps = kSkProducerWarps + kSkConverterWarps;
+constexpr int kSkHelperWarps = 1 + kSkConverterWarps;  // the producer and the converters
 constexpr int kSkHeaderBytes = 512;
-constexpr int kSkMaxStages = 8;
+constexpr int kSkMaxStages = 12;
 
 struct SkinnyHeader {
-  uint64_t full[kSkMaxStages];   // weights of the stage have landed and its activations are converted
+  uint64_t landed[kSkMaxStages]; // the stage's two TMA boxes (weights, activations) have arrived
+  uint64_t full[kSkMaxStages];   // ... and the activations are widened
   uint64_t empty[kSkMaxStages];  // every compute warp is done with the stage
   uint32_t abort;
   uint32_t last;
 };
 static_assert(sizeof(SkinnyHeader) <= kSkHeaderBytes, "header too large");
 
-// Accumulator registers decide how many compute warps a CTA may have: R * MT packed sums per thread.
+// Registers decide how many compute warps a CTA may have: a thread carries R * MT packed sums. Registers are handed
+// out per four warps, so 16 warps in all leave 128 per thread and 12 leave 168.
 template <int MT, int R>
 struct SkinnyGeo {
-  static constexpr int kMaxComputeWarps = R * MT > 16 ? 8 : 16;
+  static constexpr int kMaxComputeWarps = (R * MT >= 16 ? 12 : 16) - kSkHelperWarps;
   static constexpr int kMaxThreads = (kMaxComputeWarps + kSkHelperWarps) * 32;
 };
 
@@ -73,13 +80,6 @@ __device__ __forceinline__ float sk_hi(uint32_t w) {
   else return __uint_as_float(w & 0xffff0000u);
 }
 
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy)
-      : "memory");
-}
-
 template <bool F16>
 __device__ __forceinline__ void sk_emit(const SkinnyDev& p, int m, int n, float v) {
   const int64_t at = (int64_t)m * p.ldy + n;
@@ -88,9 +88,88 @@ __device__ __forceinline__ void sk_emit(const SkinnyDev& p, int m, int n, float 
   else static_cast<__nv_bfloat16*>(p.y)[at] = __float2bfloat16_rn(v);
 }
 
+// One round (LPR vectors of K) of one thread: its two vectors of up to R rows against the widened activations.
+// Element order inside a sum: the 8 elements of the vector, in order (q = element pair, then low, then high).
+// xs points at the round's first 16-byte entry for this thread: entry ((m * 4 + q) * HP) further on holds
+// {a[2q], b[2q], a[2q+1], b[2q+1]} of token m, a / b = the thread's first / second vector.
+//
+// Fast body: exactly L live row groups, exactly MT tokens, every vector inside the split - no predicate anywhere, so
+// nothing is issued that does not count. wsrc points at the thread's first vector of the round in its first row group;
+// group_stride steps to the next group; the second vector lies `second` bytes on.
+template <int MT, int R, int L, int HP, bool F16>
+__device__ __forceinline__ void sk_round_fast(const uint8_t* wsrc, int group_stride, int second, const float4* xs,
+                                              float2 (&acc)[R][MT]) {
+  uint4 ra[L], rb[L];
+#pragma unroll
+  for (int u = 0; u < L; ++u) {
+    ra[u] = *reinterpret_cast<const uint4*>(wsrc + (size_t)u * group_stride);
+    rb[u] = *reinterpret_cast<const uint4*>(wsrc + (size_t)u * group_stride + second);
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float2 w0[L], w1[L];
+#pragma unroll
+    for (int u = 0; u < L; ++u) {
+      const uint32_t aw = q == 0 ? ra[u].x : q == 1 ? ra[u].y : q == 2 ? ra[u].z : ra[u].w;
+      const uint32_t bw = q == 0 ? rb[u].x : q == 1 ? rb[u].y : q == 2 ? rb[u].z : rb[u].w;
+      w0[u] = make_float2(sk_lo<F16>(aw), sk_lo<F16>(bw));
+      w1[u] = make_float2(sk_hi<F16>(aw), sk_hi<F16>(bw));
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const float4 xv = xs[(m * 4 + q) * HP];
+#pragma unroll
+      for (int u = 0; u < L; ++u) acc[u][m] = __ffma2_rn(w0[u], make_float2(xv.x, xv.y), acc[u][m]);
+#pragma unroll
+      for (int u = 0; u < L; ++u) acc[u][m] = __ffma2_rn(w1[u], make_float2(xv.z, xv.w), acc[u][m]);
+    }
+  }
+}
+
+// Guarded body for everything else: fewer than MT tokens, or the last, partial round of a split, whose vectors past
+// the split's end are neutralised (weights -0 here, activations +0 by the converters: fma(-0, +0, s) = s for every s).
+template <int MT, int R, int HP, bool F16>
+__device__ __forceinline__ void sk_round_guarded(const uint8_t* wsrc, int group_stride, int second, const float4* xs,
+                                                 int nlive, int M, bool a_off, bool b_off, float2 (&acc)[R][MT]) {
+  uint4 ra[R], rb[R];
+#pragma unroll
+  for (int u = 0; u < R; ++u) {
+    ra[u] = rb[u] = make_uint4(0x80008000u, 0x80008000u, 0x80008000u, 0x80008000u);
+    if (u < nlive) {
+      if (!a_off) ra[u] = *reinterpret_cast<const uint4*>(wsrc + (size_t)u * group_stride);
+      if (!b_off) rb[u] = *reinterpret_cast<const uint4*>(wsrc + (size_t)u * group_stride + second);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float2 w0[R], w1[R];
+#pragma unroll
+    for (int u = 0; u < R; ++u) {
+      const uint32_t aw = q == 0 ? ra[u].x : q == 1 ? ra[u].y : q == 2 ? ra[u].z : ra[u].w;
+      const uint32_t bw = q == 0 ? rb[u].x : q == 1 ? rb[u].y : q == 2 ? rb[u].z : rb[u].w;
+      w0[u] = make_float2(sk_lo<F16>(aw), sk_lo<F16>(bw));
+      w1[u] = make_float2(sk_hi<F16>(aw), sk_hi<F16>(bw));
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      if (m < M) {
+        const float4 xv = xs[(m * 4 + q) * HP];
+#pragma unroll
+        for (int u = 0; u < R; ++u) {
+          if (u < nlive) {
+            acc[u][m] = __ffma2_rn(w0[u], make_float2(xv.x, xv.y), acc[u][m]);
+            acc[u][m] = __ffma2_rn(w1[u], make_float2(xv.z, xv.w), acc[u][m]);
+          }
+        }
+      }
+    }
+  }
+}
+
 // MT: token capacity (M <= MT). R: row groups a warp carries at once. LPR: virtual lanes per row (order contract).
 template <int MT, int R, int LPR, bool F16>
-__global__ void __launch_bounds__(SkinnyGeo<MT, R>::kMaxThreads, 1) skinny_stream_kernel(const SkinnyDev p) {
+__global__ void __launch_bounds__(SkinnyGeo<MT, R>::kMaxThreads, 1)
+skinny_stream_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const SkinnyDev p) {
   constexpr int HP = LPR / 2;   // threads per row; each owns virtual lanes pp and pp + HP
   constexpr int RS = 32 / HP;   // rows a warp works on side by side
   extern __shared__ __align__(128) uint8_t sk_smem[];
@@ -113,36 +192,53 @@ __global__ void __launch_bounds__(SkinnyGeo<MT, R>::kMaxThreads, 1) skinny_strea
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(smem_u32(&hdr->full[s]), 1 + kSkConverterWarps);
+      mbar_init(smem_u32(&hdr->landed[s]), 1);
+      mbar_init(smem_u32(&hdr->full[s]), kSkConverterWarps);
       mbar_init(smem_u32(&hdr->empty[s]), (uint32_t)NC);
     }
     hdr->abort = 0u;
     hdr->last = 0u;
     mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
   }
   __syncthreads();
   pdl_trigger();  // one wave by construction: the next kernel's CTAs may take the SMs as they free up
 
   if (warp == 0) {
-    // ================================ weight producer ================================
-    const uint64_t pol = policy_evict_first();
-    const uint16_t* const wbase = static_cast<const uint16_t*>(p.w);
+    // ================================ producer: weights and activations ================================
+    // The warp walks the loop together; one elected lane issues. A box is always transferred whole (rows or K past
+    // the tensor read as zero, rows past this CTA's range are the neighbour's and are never used), so the byte count
+    // a stage waits for is constant.
+    const bool leader = elect_one();
+    const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+    const uint32_t tx = (uint32_t)(p.w_box_bytes + p.x_box_bytes);
+    auto load_w = [&](int g) {
+      const int pass = g / nst, st = g - pass * nst, s = g % S;
+      const uint32_t bar = smem_u32(&hdr->landed[s]);
+      mbar_expect_tx(bar, tx);  // the activations follow (load_x)
+      tma_load_2d(smem_u32(stage0 + (size_t)s * p.stage_bytes), &tmW, bar, (vbeg + st * J * LPR) * 4, rb + pass * p.rows_pass, pol_w);
+    };
+    auto load_x = [&](int g) {
+      const int st = g % nst, s = g % S;
+      tma_load_2d(smem_u32(stage0 + (size_t)s * p.stage_bytes + p.xraw_off), &tmX, smem_u32(&hdr->landed[s]),
+                  (vbeg + st * J * LPR) * 4, 0, pol_x);
+    };
+    // fill the ring with weights, which never depend on the previous kernel; its output x follows after the wait
+    const int npre = total < S ? total : S;
+    if (leader)
+      for (int g = 0; g < npre; ++g) load_w(g);
+    pdl_wait();
+    if (leader)
+      for (int g = 0; g < npre; ++g) load_x(g);
     bool ok = true;
-    for (int g = 0; g < total; ++g) {
-      const int s = g % S, pass = g / nst, st = g - pass * nst;
-      if (g >= S) {
-        ok = mbar_wait(smem_u32(&hdr->empty[s]), ((g / S) & 1) ^ 1, abort_word);
-        if (!ok) break;
+    for (int g = npre; g < total; ++g) {
+      ok = mbar_wait(smem_u32(&hdr->empty[g % S]), ((g / S) & 1) ^ 1, abort_word);
+      if (!ok) break;
+      if (leader) {
+        load_w(g);
+        load_x(g);
       }
-      const int r0 = pass * p.rows_pass, nr = min(p.rows_pass, nrows - r0);
-      const int v0 = vbeg + st * J * LPR;
-      const uint32_t bytes = (uint32_t)min(J * LPR, vend - v0) * 16u;
-      const uint32_t bar = smem_u32(&hdr->full[s]);
-      if (lane == 0) mbar_expect_tx(bar, (uint32_t)nr * bytes);
-      __syncwarp();
-      const uint32_t dst0 = smem_u32(stage0 + (size_t)s * p.stage_bytes);
-      for (int i = lane; i < nr; i += 32)
-        bulk_copy_g2s(dst0 + (uint32_t)(i * p.pitch), wbase + (int64_t)(rb + r0 + i) * p.ldw + (int64_t)v0 * 8, bytes, bar, pol);
     }
     if (!ok) {
       if (lane == 0) atomicCAS(p.status, 0u, (unsigned)ST_SKINNY_PRODUCER_WAIT);
@@ -151,34 +247,30 @@ __global__ void __launch_bounds__(SkinnyGeo<MT, R>::kMaxThreads, 1) skinny_strea
       while (clock64() - t0 < 4000000ll) {}
     }
     __syncwarp();
-    pdl_wait();
     l2_prefetch_share(p.pf, p.pf_bytes, blockIdx.x + (int64_t)gridDim.x * blockIdx.y, (int64_t)gridDim.x * gridDim.y, lane, 32);
   } else if (warp < kSkHelperWarps) {
     // ================================ activation converters ================================
-    // Stage layout of x: for round j, token m, element pair q (elements 2q, 2q+1) and thread pp of a row, 16 bytes
-    // {a[2q], b[2q], a[2q+1], b[2q+1]} in fp32, a = vector of virtual lane pp, b = that of lane pp + HP.
-    pdl_wait();
-    const int ct = (warp - kSkProducerWarps) * 32 + lane;
+    // Widened layout of a stage's x: for round j, token m, element pair q and thread pp of a row, 16 bytes
+    // {a[2q], b[2q], a[2q+1], b[2q+1]} in fp32, a = vector of virtual lane pp, b = that of lane pp + HP; vectors past
+    // the split's end become +0.
+    const int ct = (warp - 1) * 32 + lane;
     constexpr int kCt = kSkConverterWarps * 32;
-    const uint16_t* const xbase = static_cast<const uint16_t*>(p.x);
     bool ok = true;
     for (int g = 0; g < total; ++g) {
       const int s = g % S, st = g % nst;
-      if (g >= S) {
-        ok = mbar_wait(smem_u32(&hdr->empty[s]), ((g / S) & 1) ^ 1, abort_word);
-        if (!ok) break;
-      }
+      ok = mbar_wait(smem_u32(&hdr->landed[s]), (g / S) & 1, abort_word);
+      if (!ok) break;
       const int v0 = vbeg + st * J * LPR;
       const int jn = min(J, nrounds - st * J);
+      const uint8_t* const raw = stage0 + (size_t)s * p.stage_bytes + p.xraw_off;
       float4* const xs = reinterpret_cast<float4*>(stage0 + (size_t)s * p.stage_bytes + p.xslot_off);
       const int items = jn * M * HP;
       for (int it = ct; it < items; it += kCt) {
         const int pp = it % HP, jm = it / HP, m = jm % M, j = jm / M;
-        const int va = v0 + j * LPR + pp, vb = va + HP;
-        const uint16_t* const row = xbase + (int64_t)m * p.ldx;
+        const int la = j * LPR + pp, lb = la + HP;  // vectors counted from the stage's start
         uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
-        if (va < vend) a = *reinterpret_cast<const uint4*>(row + (int64_t)va * 8);
-        if (vb < vend) b = *reinterpret_cast<const uint4*>(row + (int64_t)vb * 8);
+        if (v0 + la < vend) a = *reinterpret_cast<const uint4*>(raw + (size_t)m * p.xraw_pitch + (size_t)la * 16);
+        if (v0 + lb < vend) b = *reinterpret_cast<const uint4*>(raw + (size_t)m * p.xraw_pitch + (size_t)lb * 16);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q)
@@ -209,56 +301,39 @@ __global__ void __launch_bounds__(SkinnyGeo<MT, R>::kMaxThreads, 1) skinny_strea
 
       for (int st = 0; st < nst; ++st) {
         const int g = pass * nst + st, s = g % S;
-        ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word);
+        // the converters' arrival says the activations are widened; the TMA barrier itself makes the weights, written
+        // by the copy engine, visible to this thread
+        ok = mbar_wait(smem_u32(&hdr->full[s]), (g / S) & 1, abort_word) &&
+             mbar_wait(smem_u32(&hdr->landed[s]), (g / S) & 1, abort_word);
         if (!ok) break;
         const uint8_t* const wst = stage0 + (size_t)s * p.stage_bytes;
-        const float4* const xs = reinterpret_cast<const float4*>(wst + p.xslot_off);
+        const float4* const xs0 = reinterpret_cast<const float4*>(wst + p.xslot_off) + pp;
         const int v0 = vbeg + st * J * LPR;
         const int jn = nlive > 0 ? min(J, nrounds - st * J) : 0;  // a warp without rows only hands the stage back
-        for (int j = 0; j < jn; ++j) {
-          uint4 ra[R], rbv[R];
-#pragma unroll
-          for (int u = 0; u < R; ++u) {
-            ra[u] = rbv[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (u < nlive) {
-              const uint8_t* const src = wst + (size_t)(((u * NC + cw) * RS + rl) * p.pitch) + (size_t)(j * LPR + pp) * 16;
-              ra[u] = *reinterpret_cast<const uint4*>(src);
-              rbv[u] = *reinterpret_cast<const uint4*>(src + HP * 16);
+        // rounds whose vectors all lie inside the split take the unguarded body when every token slot is in use
+        const int jfull = min(jn, (vend - v0) / LPR);
+        const uint8_t* const wsrc0 = wst + (size_t)((cw * RS + rl) * p.pitch) + (size_t)pp * 16;
+        const int group_stride = NC * RS * p.pitch;
+        const int xround = M * 4 * HP;  // 16-byte entries of widened activations per round
+        int j = 0;
+        if (M == MT) {
+          for (; j < jfull; ++j) {
+            const uint8_t* const wsrc = wsrc0 + (size_t)j * (LPR * 16);
+            const float4* const xs = xs0 + (size_t)j * xround;
+            if (nlive == 1) sk_round_fast<MT, R, 1, HP, F16>(wsrc, group_stride, HP * 16, xs, acc);
+            if constexpr (R >= 2) {
+              if (nlive == 2) sk_round_fast<MT, R, 2, HP, F16>(wsrc, group_stride, HP * 16, xs, acc);
+            }
+            if constexpr (R >= 4) {
+              if (nlive == 3) sk_round_fast<MT, R, 3, HP, F16>(wsrc, group_stride, HP * 16, xs, acc);
+              if (nlive == 4) sk_round_fast<MT, R, 4, HP, F16>(wsrc, group_stride, HP * 16, xs, acc);
             }
           }
-          if (v0 + (j + 1) * LPR > vend) {  // last, partial round of the split: neutralise what lies past its end
-            const int va = v0 + j * LPR + pp;
-            const uint4 nz = make_uint4(0x80008000u, 0x80008000u, 0x80008000u, 0x80008000u);
-#pragma unroll
-            for (int u = 0; u < R; ++u) {
-              if (va >= vend) ra[u] = nz;
-              if (va + HP >= vend) rbv[u] = nz;
-            }
-          }
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float2 w0[R], w1[R];
-#pragma unroll
-            for (int u = 0; u < R; ++u) {
-              const uint32_t aw = q == 0 ? ra[u].x : q == 1 ? ra[u].y : q == 2 ? ra[u].z : ra[u].w;
-              const uint32_t bw = q == 0 ? rbv[u].x : q == 1 ? rbv[u].y : q == 2 ? rbv[u].z : rbv[u].w;
-              w0[u] = make_float2(sk_lo<F16>(aw), sk_lo<F16>(bw));
-              w1[u] = make_float2(sk_hi<F16>(aw), sk_hi<F16>(bw));
-            }
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-              if (m < M) {
-                const float4 xv = xs[((j * M + m) * 4 + q) * HP + pp];
-#pragma unroll
-                for (int u = 0; u < R; ++u) {
-                  if (u < nlive) {
-                    acc[u][m] = __ffma2_rn(w0[u], make_float2(xv.x, xv.y), acc[u][m]);
-                    acc[u][m] = __ffma2_rn(w1[u], make_float2(xv.z, xv.w), acc[u][m]);
-                  }
-                }
-              }
-            }
-          }
+        }
+        for (; j < jn; ++j) {
+          const int va = v0 + j * LPR + pp;  // this thread's first vector of the round
+          sk_round_guarded<MT, R, HP, F16>(wsrc0 + (size_t)j * (LPR * 16), group_stride, HP * 16, xs0 + (size_t)j * xround, nlive, M,
+                                           va >= vend, va + HP >= vend, acc);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&hdr->empty[s]));
@@ -347,20 +422,42 @@ __global__ void __launch_bounds__(SkinnyGeo<MT, R>::kMaxThreads, 1) skinny_strea
 
 inline int sk_bucket(int m) { return m <= 1 ? 1 : m <= 2 ? 2 : m <= 4 ? 4 : m <= 8 ? 8 : 16; }
 
+// Opts the kernel in to large dynamic shared memory once per device (one bit per device, set atomically; the flag is
+// a static of this template, so every kernel has its own), then launches it.
+template <auto Kernel>
+cudaError_t sk_go(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, dim3 cluster, const CUtensorMap& tw,
+                  const CUtensorMap& tx, const SkinnyDev& p) {
+  static std::atomic<uint64_t> done{0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !((done.load(std::memory_order_acquire) >> dev) & 1ull)) {
+    e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
+  }
+  return launch_ex(Kernel, grid, block, smem, stream, pdl, cluster, tw, tx, p);
+}
+
 // Geometry of one launch. `rows`, `unroll`, `warps` are the caller's tile knobs (they never change a result bit):
 //   rows   -> row groups a warp carries at once (clamped so that rows * token bucket <= 32 packed sums per thread)
-//   unroll -> rounds of LPR vectors per pipeline stage (unroll / 2)
-//   warps  -> compute warps per CTA (2 * warps, at most 8 when a thread carries more than 16 packed sums)
+//   unroll -> rounds of LPR vectors per pipeline stage (unroll / 2, at most 1 KB of K per row and stage)
+//   warps  -> warps per CTA (2 * warps, three of them helpers; at most 16, or 12 when a thread carries 16 or more
+//             packed sums); up to 8 warps per CTA two CTAs share an SM
 template <int MT, int R, int LPR>
 cudaError_t sk_launch_one(const SkinnyDev& in, int unroll, int warps, bool f16, bool pdl, cudaStream_t stream) {
   constexpr int HP = LPR / 2, RS = 32 / HP;
   SkinnyDev p = in;
   const int sms = sm_count() > 0 ? sm_count() : 1;
-  int nc = 2 * warps;
+  // 2 * warps warps per CTA, three of them helpers. CTAs of at most 8 warps run two to an SM (registers and shared
+  // memory are budgeted for it): the ring of one streams while the other computes or finishes, and in a chain of
+  // dependent launches the next kernel's CTAs fill their rings beside the last CTAs of this one.
+  int nc = 2 * warps - kSkHelperWarps;
   if (nc > SkinnyGeo<MT, R>::kMaxComputeWarps) nc = SkinnyGeo<MT, R>::kMaxComputeWarps;
   if (nc < 1) nc = 1;
+  const int occ = nc + kSkHelperWarps <= 8 ? 2 : 1;
   // one wave of CTAs; a range is never empty; with the workspace split-K one counter per range must exist
-  int64_t gx = sms / p.ksplit;
+  int64_t gx = (int64_t)sms * occ / p.ksplit;
   if (gx < 1) gx = 1;
   if (gx > p.N) gx = p.N;
   if (p.ksplit > 1 && !p.cluster && gx > in.max_ranges) gx = in.max_ranges;
@@ -373,49 +470,47 @@ cudaError_t sk_launch_one(const SkinnyDev& in, int unroll, int warps, bool f16, 
   }
   const int range = (int)((p.N + gx - 1) / gx);
   const int parked = p.cluster ? (range * p.M * 4 + 127) / 128 * 128 : 0;
-  int rows_pass = nc * RS * R;
-  if (rows_pass > range) rows_pass = range;
   int J = unroll / 2 < 1 ? 1 : unroll / 2;
-  const int budget = 200 * 1024 - kSkHeaderBytes - parked;
-  auto stage_bytes_of = [&](int rp, int j) {
-    const int pitch = j * LPR * 16 + (LPR == 8 ? 64 : 0);
-    return (rp * pitch + 127) / 128 * 128 + j * p.M * LPR * 32;
-  };
-  while (J > 1 && 2 * stage_bytes_of(rows_pass, J) > budget) J >>= 1;
+  if (J * LPR > 64) J = 64 / LPR;  // a TMA box is at most 256 four-byte elements wide
+  const int budget = (occ == 2 ? 107 : 216) * 1024 - kSkHeaderBytes - parked;
+  // a stage: the weight box (whole row groups, so that lanes of a partly filled group stay inside it), the activation
+  // box, and the activations widened to fp32
+  auto w_bytes_of = [&](int rp, int j) { return ((rp + RS - 1) / RS * RS * j * LPR * 16 + 127) / 128 * 128; };
+  auto x_bytes_of = [&](int j) { return (p.M * j * LPR * 16 + 127) / 128 * 128; };
+  auto stage_bytes_of = [&](int rp, int j) { return w_bytes_of(rp, j) + x_bytes_of(j) + j * p.M * LPR * 32; };
+  // passes of equal length, so one box height serves them all
+  int cap = nc * RS * R;
+  if (cap > 256) cap = 256;
+  int npass = (range + cap - 1) / cap;
+  int rows_pass = (range + npass - 1) / npass;
+  while (J > 1 && 3 * stage_bytes_of(rows_pass, J) > budget) J >>= 1;
   while (rows_pass > RS && 2 * stage_bytes_of(rows_pass, J) > budget) rows_pass = (rows_pass + 1) / 2;
   if (2 * stage_bytes_of(rows_pass, J) > budget) return cudaErrorInvalidConfiguration;
   p.rounds = J;
   p.rows_pass = rows_pass;
-  p.pitch = J * LPR * 16 + (LPR == 8 ? 64 : 0);
-  p.xslot_off = (rows_pass * p.pitch + 127) / 128 * 128;
+  p.pitch = J * LPR * 16;
+  p.xraw_off = w_bytes_of(rows_pass, J);
+  p.xraw_pitch = J * LPR * 16;
+  p.xslot_off = p.xraw_off + x_bytes_of(J);
   p.stage_bytes = stage_bytes_of(rows_pass, J);
+  p.w_box_bytes = rows_pass * p.pitch;
+  p.x_box_bytes = p.M * p.xraw_pitch;
+  // as deep as shared memory allows: the ring is what keeps enough bytes in flight per SM to cover the loaded latency
+  // of HBM (about 2 us at full rate, some 90 KB per SM)
   int S = budget / p.stage_bytes;
-  // no deeper than what hides the memory latency: about 96 KB in flight per SM is plenty, and a smaller CTA lets the
-  // next kernel of a dependent chain become resident beside this one
-  const int want = (96 * 1024 + p.stage_bytes - 1) / p.stage_bytes;
-  if (S > want) S = want < 3 ? 3 : want;
-  if (S > budget / p.stage_bytes) S = budget / p.stage_bytes;
   if (S > kSkMaxStages) S = kSkMaxStages;
   if (S < 2) return cudaErrorInvalidConfiguration;
   p.stages = S;
+  // tensor maps over four-byte elements: box = chunk x rows, dense rows in shared memory, zero fill outside the tensor
+  CUtensorMap tw, tx;
+  if (!make_dense_map(&tw, p.w, (int64_t)p.K * 2, p.N, p.ldw * 2, p.pitch, rows_pass, true) ||
+      !make_dense_map(&tx, p.x, (int64_t)p.K * 2, p.M, p.ldx * 2, p.xraw_pitch, p.M, false))
+    return cudaErrorInvalidValue;
   const size_t smem = (size_t)kSkHeaderBytes + (size_t)S * p.stage_bytes + parked;
   const dim3 grid((unsigned)gx, (unsigned)p.ksplit), block((unsigned)((nc + kSkHelperWarps) * 32));
   const dim3 cluster(1, p.cluster ? (unsigned)p.ksplit : 1u, 1);
-  auto go = [&](auto kernel) -> cudaError_t {
-    // opt in to large dynamic shared memory once per kernel and device (one bit per device, set atomically)
-    static std::atomic<uint64_t> done{0};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !(done.load(std::memory_order_acquire) >> dev & 1ull)) {
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-      if (e != cudaSuccess) return e;
-      if (dev >= 0 && dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
-    }
-    return launch_ex(kernel, grid, block, smem, stream, pdl, cluster, p);
-  };
-  if (f16) return go(skinny_stream_kernel<MT, R, LPR, true>);
-  return go(skinny_stream_kernel<MT, R, LPR, false>);
+  if (f16) return sk_go<skinny_stream_kernel<MT, R, LPR, true>>(grid, block, smem, stream, pdl, cluster, tw, tx, p);
+  return sk_go<skinny_stream_kernel<MT, R, LPR, false>>(grid, block, smem, stream, pdl, cluster, tw, tx, p);
 }
 
 template <int MT, int LPR>

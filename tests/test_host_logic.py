@@ -137,12 +137,11 @@ def test_heuristics_fill_the_gpu():
     assert L.default_tc_choice("w4a16_bf16", 4, 28672, 8192, sms).cfg == 0  # two atoms do not fit for W4A16
     for m in (1, 16, 64, 256):
         assert L.default_tc_choice("fp8", m, 1280, 8192, sms).ksplit <= 8
-    # skinny engine: one wave of CTAs, each with a row range that one pass of its warps covers
+    # skinny engine: one wave of small CTAs, two to an SM, each with a contiguous row range
     o = L.default_skinny_order(11008, 4096, sms)
-    assert o.lanes_per_row == 16 and o.ksplit == 1 and L.skinny_ranges(11008, o.ksplit, sms) == sms
-    assert -(-11008 // sms) <= 16 * (64 // o.lanes_per_row) * o.default_tile.rows
+    assert o.lanes_per_row == 32 and o.ksplit == 1 and L.skinny_ranges(11008, o.ksplit, sms) == 2 * sms
     small = L.default_skinny_order(96, 2560, sms)
-    assert small.ksplit > 1 and small.cluster and L.skinny_ranges(96, small.ksplit, sms) * small.ksplit <= sms
+    assert small.ksplit > 1 and small.cluster and L.skinny_ranges(96, small.ksplit, sms) * small.ksplit <= 2 * sms
     assert L.default_skinny_order(1, 8, sms).lanes_per_row == 8 and L.skinny_ranges(1, 1, sms) == 1
     plan = L.default_plan("bf16", 11008, 4096, sms)
     assert plan.skinny is not None and plan.skinny_max_m >= 1 and set(plan.tc) >= {1, 16, 256}
