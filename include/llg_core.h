@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define LLG_ABI_VERSION 1
+#define LLG_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define LLG_API __attribute__((visibility("default")))
@@ -203,6 +203,39 @@ LLG_API int llg_allreduce_quant_fp8(const void* const* buffers_dev, uint32_t* co
                                     int64_t ldq, float* scale_out, int32_t rows, int32_t cols, int32_t dtype,
                                     float min_scale, int32_t rank, int32_t world, void* stream);
 
+/* Row-parallel GEMM of a tensor-parallel layer with the all-reduce's transfer inside its epilogue ("push"): every
+ * finished output element is stored, with plain stores into peer-mapped memory, to dst[d] for every rank d - the place
+ * where rank d collects this rank's partial, laid out like y - instead of to args->y (which is ignored), so the bytes
+ * cross NVLink while the remaining tiles are still being computed. When the whole grid has finished, its last CTA adds 1
+ * to flags[d][row * world + rank] for every rank d and token row: the same arrival counters llg_allreduce_oneshot uses,
+ * sent one way. The consumer on every rank is llg_reduce_local. `done` is a zero-initialised counter local to this
+ * rank that the kernel returns to zero. rows = the GEMM's token count (<= LLG_AR_MAX_CTAS); world <= 8. Consecutive
+ * pushes must alternate between two destination buffers, as with llg_allreduce_oneshot. No multicast, no TMA on peer
+ * memory. No counterpart in the reference (it has no multi-GPU code); SURVEY-level analogue: the row-parallel
+ * projections of tools/decode_step.py:27-40 followed by the framework's all-reduce. */
+typedef struct llg_push_args {
+  int32_t world, rank, rows, reserved;
+  void* dst[8];
+  uint32_t* flags[8];
+  uint32_t* done;
+} llg_push_args;
+
+LLG_API int llg_tc_gemm_push(const llg_tc_args* args, const llg_push_args* push, void* stream);
+
+/* Consumer of pushed partials, one CTA per token row: waits (bounded) until all `world` ranks have signalled the row,
+ * adds the local copies recv + src * region_bytes in rank order in fp32 and rounds to the 16-bit type - bit for bit the
+ * result of llg_allreduce_oneshot - then optionally adds `residual` (fp32 add, one rounding), stores the row to `out`
+ * (may be NULL when q is given) and, when q is given, quantizes it per token to FP8 exactly as llg_quant does
+ * (scale_out[rows], q [rows, ldq]). `flags` are THIS rank's flag words. No counterpart in the reference. */
+LLG_API int llg_reduce_local(const void* recv, int64_t region_bytes, uint32_t* flags, void* out, const void* residual,
+                             void* q, int64_t ldq, float* scale_out, int32_t rows, int32_t cols, int32_t dtype,
+                             float min_scale, int32_t world, void* stream);
+
+/* Bound, in GPU clock cycles, of every wait for a peer's signal in the all-reduce kernels (default about one second;
+ * cycles <= 0 restores it). Process-wide, read at launch. Meant for failure tests and for deployments that want a
+ * stalled peer reported sooner; after an expired wait llg_device_status() returns 16. No counterpart in the reference. */
+LLG_API void llg_set_wait_limit(int64_t cycles);
+
 /* Split-K tensor-core GEMM for callers that must not allocate device memory. Same arguments and result as
  * llg_tc_gemm, except that args->ws / args->counters are ignored: partial sums and arrival counters live in a fixed
  * scratch array inside the library (LLG_STATIC_WS_ELEMS 4-byte partials + LLG_STATIC_COUNTERS counters, about 4 MB,
@@ -223,9 +256,10 @@ LLG_API int llg_allreduce_quant_fp8(const void* const* buffers_dev, uint32_t* co
 #define LLG_STATIC_COUNTERS 4096
 LLG_API int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream);
 
-/* sizeof(llg_skinny_args), sizeof(llg_tc_args), sizeof(llg_quant_args) as this library was compiled: lets a foreign-
- * function binding verify its struct layout before the first call. No counterpart in the reference. */
-LLG_API void llg_struct_sizes(int32_t out[3]);
+/* sizeof of llg_skinny_args, llg_tc_args, llg_quant_args, llg_gated_quant_args, llg_push_args as this library was
+ * compiled: lets a foreign-function binding verify its struct layout before the first call. No counterpart in the
+ * reference. */
+LLG_API void llg_struct_sizes(int32_t out[5]);
 
 LLG_API const char* llg_last_error(void);
 LLG_API int32_t llg_abi_version(void);

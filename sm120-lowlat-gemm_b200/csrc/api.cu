@@ -134,32 +134,41 @@ bool make_dense_map(CUtensorMap* m, const void* ptr, int64_t row_bytes, int64_t 
 
 bool pdl_on() { return g_pdl.load(std::memory_order_relaxed); }
 
-int sm_count() {
-  static int counts[64] = {};
+// Per-device facts, looked up once per device. Concurrent first use from several threads is harmless: every thread
+// computes the same value and the slots are atomics.
+static int cached_attr(std::atomic<int>* slots, cudaDeviceAttr attr) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-  if (counts[dev] == 0) cudaDeviceGetAttribute(&counts[dev], cudaDevAttrMultiProcessorCount, dev);
-  return counts[dev];
+  int v = slots[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    cudaDeviceGetAttribute(&v, attr, dev);
+    slots[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+int sm_count() {
+  static std::atomic<int> counts[64];
+  return cached_attr(counts, cudaDevAttrMultiProcessorCount);
 }
 
 int64_t l2_bytes() {
-  static int sizes[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-  if (sizes[dev] == 0) cudaDeviceGetAttribute(&sizes[dev], cudaDevAttrL2CacheSize, dev);
-  return sizes[dev];
+  static std::atomic<int> sizes[64];
+  return cached_attr(sizes, cudaDevAttrL2CacheSize);
 }
 
 unsigned int* status_word_device_ptr() {
-  static unsigned int* ptrs[64] = {};
+  static std::atomic<unsigned int*> ptrs[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!ptrs[dev]) {
+  unsigned int* ptr = ptrs[dev].load(std::memory_order_acquire);
+  if (!ptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
-    ptrs[dev] = static_cast<unsigned int*>(p);
+    ptr = static_cast<unsigned int*>(p);
+    ptrs[dev].store(ptr, std::memory_order_release);
   }
-  return ptrs[dev];
+  return ptr;
 }
 
 TcTile tc_tile_of(int cfg) {
@@ -227,11 +236,14 @@ int32_t llg_abi_version(void) { return LLG_ABI_VERSION; }
 void llg_set_pdl(int32_t on) { g_pdl.store(on != 0, std::memory_order_relaxed); }
 int32_t llg_pdl_enabled(void) { return g_pdl.load(std::memory_order_relaxed) ? 1 : 0; }
 int32_t llg_smem_budget(void) { return kSmemBudget; }
-void llg_struct_sizes(int32_t out[3]) {
+void llg_struct_sizes(int32_t out[5]) {
   out[0] = (int32_t)sizeof(llg_skinny_args);
   out[1] = (int32_t)sizeof(llg_tc_args);
   out[2] = (int32_t)sizeof(llg_quant_args);
+  out[3] = (int32_t)sizeof(llg_gated_quant_args);
+  out[4] = (int32_t)sizeof(llg_push_args);
 }
+void llg_set_wait_limit(int64_t cycles) { set_ar_spin_cycles(cycles > 0 ? cycles : 2000000000ll); }
 
 int llg_device_status(uint32_t* status) {
   unsigned int* dptr = status_word_device_ptr();
@@ -336,7 +348,8 @@ static int check_operand(const void* ptr, int64_t ld_bytes, const char* name) {
   return 0;
 }
 
-int llg_tc_gemm(const llg_tc_args* a, void* stream) {
+// validate_only: every check of the call, no tensor map, no launch
+static int tc_gemm_run(const llg_tc_args* a, const llg_push_args* push, void* stream, bool validate_only = false) {
   if (!a) return fail(LLG_E_INVALID, "null arguments");
   KindSpec ks;
   if (!kind_spec(a->kind, &ks)) return fail(LLG_E_INVALID, "unknown kind %d", a->kind);
@@ -350,7 +363,17 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
   if (K <= 0 || K % ks.k_align)
     return fail(LLG_E_INVALID, "K must be a positive multiple of %d for this kind, got %lld", ks.k_align, (long long)K);
   if (P < 1 || Q < 1 || P > INT32_MAX || Q > INT32_MAX || K > INT32_MAX) return fail(LLG_E_INVALID, "empty or too large problem");
-  if (!a->y) return fail(LLG_E_INVALID, "y must be 2-D with unit last stride");
+  if (!a->y && !push) return fail(LLG_E_INVALID, "y must be 2-D with unit last stride");
+  if (push) {
+    if (push->world < 1 || push->world > 8 || push->rank < 0 || push->rank >= push->world)
+      return fail(LLG_E_INVALID, "push: world must be in [1, 8] and rank inside it, got rank %d of %d", push->rank, push->world);
+    if (!push->done) return fail(LLG_E_INVALID, "push: the local completion counter is missing");
+    if (push->rows != (a->swap ? Q : P) || push->rows > LLG_AR_MAX_CTAS)
+      return fail(LLG_E_INVALID, "push: rows must equal the token count of the GEMM and be at most %d, got %d", LLG_AR_MAX_CTAS,
+                  push->rows);
+    for (int d = 0; d < push->world; ++d)
+      if (!push->dst[d] || !push->flags[d]) return fail(LLG_E_INVALID, "push: destination or flag pointer of rank %d is null", d);
+  }
   if (a->out_dtype < LLG_DT_BF16 || a->out_dtype > LLG_DT_F32) return fail(LLG_E_INVALID, "y must be bfloat16, float16 or float32");
   const bool mixed = a->kind >= LLG_KIND_W8A16_BF16;
   if (mixed && !a->swap) return fail(LLG_E_INVALID, "mixed-precision kinds need the weight as operand a (swap)");
@@ -398,6 +421,8 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
   if (tc_stage_bytes_of(a->kind, a->cfg) == 0)
     return fail(LLG_E_CONFIG, "config %d cannot be launched for this kind: stage does not fit shared memory", a->cfg);
 
+  if (validate_only) return LLG_OK;
+
   p.row_scale = a->row_scale; p.row_scale_len = a->row_scale_len;
   p.col_scale = a->col_scale; p.col_scale_len = a->col_scale_len;
   p.bias = a->bias; p.bias_dtype = a->bias ? a->bias_dtype : LLG_DT_NONE; p.bias_on_p = a->bias_on_p != 0;
@@ -410,6 +435,14 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
   p.pf = a->prefetch; p.pf_bytes = a->prefetch ? a->prefetch_bytes : 0;
   p.status = status_word_device_ptr();
   if (!p.status) return fail(LLG_E_CUDA, "no device status word");
+  if (push) {
+    p.push_n = push->world; p.push_rank = push->rank; p.push_rows = push->rows; p.push_done = push->done;
+    for (int d = 0; d < push->world; ++d) {
+      p.push_y[d] = push->dst[d];
+      p.push_flag[d] = push->flags[d];
+    }
+    p.y = push->dst[push->rank];
+  }
   const uint32_t bq = (uint32_t)tile.bq;
   switch (a->kind) {
     case LLG_KIND_BF16: case LLG_KIND_W8A16_BF16: case LLG_KIND_W4A16_BF16:
@@ -467,6 +500,41 @@ int llg_tc_gemm(const llg_tc_args* a, void* stream) {
     cudaGetLastError();
     return fail(e == cudaErrorInvalidConfiguration ? LLG_E_CONFIG : LLG_E_CUDA,
                 "config %d cannot be launched for this kind: %s", a->cfg, cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
+int llg_tc_gemm(const llg_tc_args* a, void* stream) { return tc_gemm_run(a, nullptr, stream); }
+
+int llg_tc_gemm_push(const llg_tc_args* a, const llg_push_args* push, void* stream) {
+  if (!push) return fail(LLG_E_INVALID, "null arguments");
+  return tc_gemm_run(a, push, stream);
+}
+
+int llg_reduce_local(const void* recv, int64_t region_bytes, uint32_t* flags, void* out, const void* residual, void* q,
+                     int64_t ldq, float* scale_out, int32_t rows, int32_t cols, int32_t dtype, float min_scale, int32_t world,
+                     void* stream) {
+  if (!recv || !flags) return fail(LLG_E_INVALID, "reduce: null pointer");
+  if (world < 1 || world > 8) return fail(LLG_E_INVALID, "reduce: world must be in [1, 8], got %d", world);
+  if (rows < 1 || rows > LLG_AR_MAX_CTAS)
+    return fail(LLG_E_INVALID, "reduce: rows must be in [1, %d] (one CTA and one flag set per row), got %d", LLG_AR_MAX_CTAS, rows);
+  if (cols < 8 || cols % 8 || cols > LLG_ARQ_MAX_COLS)
+    return fail(LLG_E_INVALID, "reduce: cols must be a multiple of 8 in [8, %d], got %d", LLG_ARQ_MAX_COLS, cols);
+  if (dtype != LLG_DT_BF16 && dtype != LLG_DT_F16) return fail(LLG_E_INVALID, "reduce: dtype must be bf16 or f16");
+  if (region_bytes < (int64_t)rows * cols * 2 || region_bytes % 16 || !aligned(recv, 16))
+    return fail(LLG_E_INVALID, "reduce: regions must be 16-byte aligned and hold rows * cols 16-bit values");
+  if ((out && !aligned(out, 16)) || (residual && !aligned(residual, 16)))
+    return fail(LLG_E_INVALID, "reduce: out and residual need 16-byte alignment");
+  if (q && (!scale_out || ldq < cols || ldq % 8 || !aligned(q, 8)))
+    return fail(LLG_E_INVALID, "reduce: q needs scale_out and 8-byte aligned rows (ldq %% 8 == 0, ldq >= cols)");
+  if (!q && !out) return fail(LLG_E_INVALID, "reduce: nothing to write (neither out nor q)");
+  unsigned* status = status_word_device_ptr();
+  if (!status) return fail(LLG_E_CUDA, "no device status word");
+  const cudaError_t e = reduce_local_launch(recv, region_bytes, flags, out, residual, q, ldq, scale_out, rows, cols, dtype,
+                                            min_scale, world, status, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LLG_E_CUDA, "reduce launch failed: %s", cudaGetErrorString(e));
   }
   return LLG_OK;
 }
@@ -539,12 +607,17 @@ int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream) {
   llg_tc_args a = *args;
   a.ws = nullptr; a.ws_elems = 0; a.counters = nullptr; a.counters_elems = 0;
   const bool cluster = a.cluster && a.ksplit > 1;
+  int64_t tiles = 0;
   if (a.ksplit > 1 && !cluster) {
+    // sizes are checked before any arithmetic on them
     const TcTile tile = tc_tile_of(a.cfg);
     if (tile.bq == 0) return fail(LLG_E_INVALID, "cfg must be in [0, %d), got %d", LLG_NUM_CFGS, a.cfg);
-    const int64_t need = (int64_t)a.ksplit * a.a_rows * a.b_rows;
-    const int64_t tiles = ((a.a_rows + 127) / 128) * ((a.b_rows + tile.bq - 1) / tile.bq);
-    if (a.a_rows < 1 || a.b_rows < 1 || need > LLG_STATIC_WS_ELEMS || tiles > LLG_STATIC_COUNTERS)
+    if (a.ksplit > 64) return fail(LLG_E_INVALID, "ksplit must be in [1, 64], got %d", a.ksplit);
+    if (a.a_rows < 1 || a.b_rows < 1 || a.a_rows > INT32_MAX || a.b_rows > INT32_MAX)
+      return fail(LLG_E_INVALID, "empty or too large problem");
+    const int64_t need = (int64_t)a.ksplit * a.a_rows * a.b_rows;  // < 2^6 * 2^31 * 2^31: no overflow
+    tiles = ((a.a_rows + 127) / 128) * ((a.b_rows + tile.bq - 1) / tile.bq);
+    if (need > LLG_STATIC_WS_ELEMS || tiles > LLG_STATIC_COUNTERS)
       return fail(LLG_E_INVALID, "static workspace too small: this GEMM needs %lld partials and %lld counters, the built-in "
                   "scratch holds %d and %d; use llg_tc_gemm with a caller-provided workspace", (long long)need,
                   (long long)tiles, LLG_STATIC_WS_ELEMS, LLG_STATIC_COUNTERS);
@@ -552,11 +625,15 @@ int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream) {
     a.ws_elems = LLG_STATIC_WS_ELEMS;
     a.counters = reinterpret_cast<int32_t*>(ptr + kStaticWsBytes);
     a.counters_elems = LLG_STATIC_COUNTERS;
+  }
+  // the whole call is validated before anything is enqueued: a refused call must not touch the shared counters
+  if (int r = tc_gemm_run(&a, nullptr, stream, true)) return r;
+  if (tiles > 0) {
     // the array keeps whatever the last call left: the counters of this launch must start at zero
     e = cudaMemsetAsync(a.counters, 0, (size_t)tiles * 4, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail("clearing the static counters", e);
   }
-  return llg_tc_gemm(&a, stream);
+  return tc_gemm_run(&a, nullptr, stream);
 }
 
 int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* x_dev, int64_t x_bytes, void* y_host,

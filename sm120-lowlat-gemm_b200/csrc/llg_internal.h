@@ -94,6 +94,13 @@ cudaError_t skinny_launch_l16(const SkinnyDev& p, int rows, int unroll, int warp
 cudaError_t skinny_launch_l32(const SkinnyDev& p, int rows, int unroll, int warps, bool f16, bool pdl, cudaStream_t s);
 
 // ---- one-shot all-reduce over peer memory ------------------------------------------------------------------------
+// Bound of every spin on a peer's signal, in clock cycles (about one second unless llg_set_wait_limit changed it).
+long long ar_spin_cycles();
+void set_ar_spin_cycles(long long cycles);
+// Consumer of the pushed partials: recv holds `world` regions (index = source rank) of [rows, cols] 16-bit values.
+cudaError_t reduce_local_launch(const void* recv, int64_t region_bytes, uint32_t* flags, void* out, const void* residual,
+                                void* q, int64_t ldq, float* scale_out, int rows, int cols, int dtype, float min_scale,
+                                int world, unsigned* status, cudaStream_t s);
 cudaError_t allreduce_launch(const void* const* buffers, uint32_t* const* flags, void* out, int64_t vecs, int rank,
                              int world, int dtype, int ctas, unsigned* status, cudaStream_t s);
 cudaError_t allreduce_quant_fp8_launch(const void* const* buffers, uint32_t* const* flags, void* out, void* q, int64_t ldq,
@@ -146,6 +153,13 @@ struct TcDev {
   int pf_pace;          // > 0: self-prefetch of later weight stages into L2, one stage per pf_pace cycles
   int pf_ahead;         // ... at most this many stages ahead of the producer
   unsigned char sf_tma;  // W4A16 / NVFP4: block scales come by TMA (third and fourth tensor map), not per-thread copies
+  // Push mode (row-parallel GEMM of a tensor-parallel layer): every finished output element is stored to push_y[d] for
+  // each of the push_n ranks d instead of to y, and the last CTA of the grid to finish signals row slot r of every
+  // rank: one add to push_flag[d][r * push_n + push_rank].
+  int push_n, push_rank, push_rows;
+  void* push_y[8];
+  uint32_t* push_flag[8];
+  unsigned* push_done;   // local counter of finished CTAs, zero between launches
 };
 
 struct TcTile {

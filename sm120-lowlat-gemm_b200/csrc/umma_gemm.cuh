@@ -21,6 +21,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "llg_internal.h"
 #include "ptx_sm100.cuh"
 
@@ -115,13 +117,24 @@ __device__ __forceinline__ float tc_finish_row(const TcDev& prm, float alpha, fl
   if (prm.bias_dtype != LLG_DT_NONE) v = __fadd_rn(v, prm.bias_on_p ? bias_p : tc_bias(prm, q));
   return v;
 }
+__device__ __forceinline__ void tc_store_to(void* y, int out_dtype, int64_t at, float v) {
+  switch (out_dtype) {
+    case LLG_DT_BF16: static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v); break;
+    case LLG_DT_F16: static_cast<__half*>(y)[at] = __float2half_rn(v); break;
+    default: static_cast<float*>(y)[at] = v; break;
+  }
+}
+// One finished output element. In push mode it goes to every rank's copy of this rank's partial (plain stores into
+// peer-mapped memory; the transfer so overlaps the tiles that are still being computed) instead of to y.
 __device__ __forceinline__ void tc_store(const TcDev& prm, int p, int q, float v) {
   const int64_t at = prm.swap ? (int64_t)q * prm.ldy + p : (int64_t)p * prm.ldy + q;
-  switch (prm.out_dtype) {
-    case LLG_DT_BF16: static_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(v); break;
-    case LLG_DT_F16: static_cast<__half*>(prm.y)[at] = __float2half_rn(v); break;
-    default: static_cast<float*>(prm.y)[at] = v; break;
+  if (prm.push_n == 0) {
+    tc_store_to(prm.y, prm.out_dtype, at, v);
+    return;
   }
+#pragma unroll
+  for (int d = 0; d < 8; ++d)
+    if (d < prm.push_n) tc_store_to(prm.push_y[d], prm.out_dtype, at, v);
 }
 
 // ---- exact widening of 8-bit / 4-bit floats to 16-bit pairs ---------------------------------------------------------
@@ -840,7 +853,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o[c] = t;
             }
             bool done = false;
-            if (!prm.swap && c0 + 16 <= nq) {
+            if (!prm.swap && c0 + 16 <= nq && prm.push_n == 0) {
               // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
               if (prm.out_dtype == LLG_DT_F32) {
                 float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
@@ -1002,6 +1015,27 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem, G::kTmemCols);
   }
+  if (prm.push_n > 0 && warp == 0) {
+    // Every output store of this CTA precedes the barrier above. Lane 0 makes them visible system-wide and counts the
+    // CTA in; the CTA that completes the count has thereby observed every other CTA's fence, resets the counter for the
+    // next launch and tells each rank, once per token row, that this rank's partial has arrived. Signals are one-way
+    // adds; nothing here waits.
+    unsigned last = 0u;
+    if (lane == 0) {
+      __threadfence_system();
+      const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
+      last = atomicAdd(prm.push_done, 1u) == ctas - 1u ? 1u : 0u;
+      if (last) atomicExch(prm.push_done, 0u);
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence_system();
+      for (int i = lane; i < prm.push_rows * prm.push_n; i += 32) {
+        const int row = i / prm.push_n, d = i - row * prm.push_n;
+        atomicAdd_system(prm.push_flag[d] + (int64_t)row * prm.push_n + prm.push_rank, 1u);
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -1024,14 +1058,14 @@ cudaError_t umma_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const 
       if (need > 227 * 1024) return cudaErrorInvalidConfiguration;
       if (smem < need) smem = need;
     }
-    static unsigned attr_done = 0;  // one bit per device
+    static std::atomic<uint64_t> attr_done{0};  // one bit per device
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev >= 32 || !(attr_done & (1u << dev))) {
+    if (dev < 0 || dev >= 64 || !((attr_done.load(std::memory_order_acquire) >> dev) & 1ull)) {
       e = cudaFuncSetAttribute(umma_gemm_kernel<FAM, BQ, ATOMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
       if (e != cudaSuccess) return e;
-      if (dev < 32) attr_done |= 1u << dev;
+      if (dev >= 0 && dev < 64) attr_done.fetch_or(1ull << dev, std::memory_order_release);
     }
     if (p.cluster || p.ksplit > 1 || p.p_rows < 8 || p.p_rows > kBP) p.p_rows = kBP;  // ragged rows only without split-K
     const int64_t tiles = (int64_t)((p.P + p.p_rows - 1) / p.p_rows) * ((p.Q + BQ - 1) / BQ);

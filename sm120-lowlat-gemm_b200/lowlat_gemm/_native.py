@@ -53,6 +53,11 @@ class GatedQuantArgs(C.Structure):
     _fields_ = [("q", QuantArgs), ("up", c_ptr), ("ldup", c_i64), ("act", c_ptr), ("ldact", c_i64)]
 
 
+class PushArgs(C.Structure):
+    _fields_ = [("world", c_i32), ("rank", c_i32), ("rows", c_i32), ("reserved", c_i32), ("dst", c_ptr * 8),
+                ("flags", c_ptr * 8), ("done", c_ptr)]
+
+
 # every symbol include/llg_core.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "llg_skinny": (c_i32, [C.POINTER(SkinnyArgs), c_ptr]),
@@ -68,13 +73,17 @@ SYMBOLS = {
     "llg_allreduce_quant_fp8": (c_i32, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i32, c_i32, c_i32, C.c_float, c_i32,
                                         c_i32, c_ptr]),
     "llg_tc_gemm_static_ws": (c_i32, [C.POINTER(TcArgs), c_ptr]),
+    "llg_tc_gemm_push": (c_i32, [C.POINTER(TcArgs), C.POINTER(PushArgs), c_ptr]),
+    "llg_reduce_local": (c_i32, [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i32, c_i32, c_i32, C.c_float, c_i32,
+                                 c_ptr]),
+    "llg_set_wait_limit": (None, [c_i64]),
     "llg_tc_gemm_host": (c_i32, [C.POINTER(TcArgs), c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_ptr]),
     "llg_device_status": (c_i32, [C.POINTER(C.c_uint32)]),
-    "llg_struct_sizes": (None, [C.POINTER(c_i32 * 3)]),
+    "llg_struct_sizes": (None, [C.POINTER(c_i32 * 5)]),
     "llg_last_error": (C.c_char_p, []),
     "llg_abi_version": (c_i32, []),
 }
-ABI_VERSION = 1
+ABI_VERSION = 2
 AR_MAX_CTAS = 64      # LLG_AR_MAX_CTAS: flag sets (CTAs, or rows of the fused all-reduce + quantizer) per all-reduce
 
 
@@ -98,9 +107,9 @@ def _load() -> C.CDLL:
         fn.restype, fn.argtypes = res, args
     if lib.llg_abi_version() != ABI_VERSION:
         raise ImportError(f"lowlat_gemm: {path} has ABI {lib.llg_abi_version()}, this package needs {ABI_VERSION}")
-    sizes = (c_i32 * 3)()
+    sizes = (c_i32 * 5)()
     lib.llg_struct_sizes(C.byref(sizes))
-    want = (C.sizeof(SkinnyArgs), C.sizeof(TcArgs), C.sizeof(QuantArgs))
+    want = (C.sizeof(SkinnyArgs), C.sizeof(TcArgs), C.sizeof(QuantArgs), C.sizeof(GatedQuantArgs), C.sizeof(PushArgs))
     if tuple(sizes) != want:
         raise ImportError(f"lowlat_gemm: struct layout mismatch, library {tuple(sizes)} vs binding {want}")
     return lib

@@ -78,10 +78,18 @@ def _default_fns():
 
 
 class DecodeStep:
-    """`layers` decode layers on this rank; run() executes them in order on the current stream."""
+    """`layers` decode layers on this rank; run() executes them in order on the current stream.
+
+    residual=True keeps the hidden state of a decoder: h = h + all_reduce(o(...)), h = h + all_reduce(down(...)).
+    comm: None (NCCL all_reduce, or no collective on one rank), or a comm.OneShotAllReduce. With a comm, `push=True`
+    sends the row-parallel projections through the push form - the GEMM's epilogue stores into every rank's buffer, one
+    consumer kernel sums, adds the residual and quantizes for the next projection - and `push=False` through the pull
+    form (separate all-reduce kernel, fused with the FP8 quantizer where `fuse_quant` allows, residual added by an
+    elementwise kernel). A single-rank comm (local=True) gives a one-GPU step the very same kernels."""
 
     def __init__(self, kind: str, layers: int, tp: int, rank: int, device, shape: LayerShape = LayerShape(), group=None,
-                 gemm_fn=None, prefetch_bytes: int = 0, nvfp4_global: float = 64.0, comm=None, fuse_quant: bool = True):
+                 gemm_fn=None, prefetch_bytes: int = 0, nvfp4_global: float = 64.0, comm=None, fuse_quant: bool = True,
+                 residual: bool = False, push: bool = False):
         self.kind, self.tp, self.rank, self.group, self.device = kind, tp, rank, group, device
         self.shape = shape
         self.layers = [DecodeLayer(kind, shape, tp, rank, device, seed=i) for i in range(layers)]
@@ -94,7 +102,10 @@ class DecodeStep:
         self.collectives = 0
         self.gemms = 0
         self.quants = 0
-        self.comm = comm if tp > 1 else None  # a comm.OneShotAllReduce, or None for NCCL all_reduce
+        self.reduces = 0  # the library's own all-reduce / local-sum kernels
+        self.comm = comm if (tp > 1 or push) else None  # a comm.OneShotAllReduce, or None for NCCL all_reduce
+        self.push = bool(push and self.comm is not None)
+        self.residual = residual
         self._ar_index = 0
         self.fuse_quant = fuse_quant  # FP8 with `comm`: all-reduce and the next activation quantizer as one kernel
 
@@ -104,16 +115,18 @@ class DecodeStep:
     def _order(self):
         return [(li, name) for li in range(len(self.layers)) for name in ("qkv", "o", "gate_up", "down")]
 
-    def _project(self, h: torch.Tensor, w, kw: dict, nxt, out=None, gated: bool = False) -> torch.Tensor:
-        """One projection: activation quantization where the precision needs it, then the GEMM. With `gated`, h is
-        [gate | up] and the projection's input is silu(gate) * up, fused into the quantizer's kernel."""
+    def _project(self, h, w, kw: dict, nxt, out=None, gated: bool = False, gemm=None) -> torch.Tensor:
+        """One projection: activation quantization where the precision needs it, then the GEMM (`gemm`, default the
+        library's gemm()). With `gated`, h is [gate | up] and the projection's input is silu(gate) * up, fused into the
+        quantizer's kernel. h may be a (q, scale) pair that an earlier fused kernel already produced."""
+        gemm = gemm or self._gemm
         extra = {} if out is None else {"out": out}
         if nxt is not None and self.prefetch_bytes:
             extra.update(prefetch=nxt, prefetch_bytes=min(self.prefetch_bytes, nxt.numel() * nxt.element_size()))
         self.gemms += 1
-        if isinstance(h, tuple):  # (q, scale): already quantized by the fused all-reduce of the previous projection
+        if isinstance(h, tuple):
             q, s = h
-            return self._gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
+            return gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
         if gated and self._api is None:  # host stand-in used by the CPU tests
             half = h.shape[1] // 2
             h, gated = torch.nn.functional.silu(h[:, :half]) * h[:, half:], False
@@ -121,32 +134,54 @@ class DecodeStep:
             self.quants += 1  # one quantizer / activation kernel of the library
         if self.kind == "fp8":
             q, s = self._api.silu_mul_quantize_fp8(h) if gated else self._q8(h)
-            return self._gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
+            return gemm(q, w, x_scale=s, out_dtype=self.act_dtype, **kw, **extra)
         if self.kind == "nvfp4":
             q, sf = self._api.silu_mul_quantize_nvfp4(h, self._g4) if gated else self._q4(h, self._g4)
-            return self._gemm(q, w, x_block_scale=sf, x_scale=1.0 / self._g4_host, out_dtype=self.act_dtype, **kw, **extra)
+            return gemm(q, w, x_block_scale=sf, x_scale=1.0 / self._g4_host, out_dtype=self.act_dtype, **kw, **extra)
         if gated:
             h = self._api.silu_mul(h)
-        return self._gemm(h, w, out_dtype=self.act_dtype, **kw, **extra)
+        return gemm(h, w, out_dtype=self.act_dtype, **kw, **extra)
 
-    def _row_parallel(self, h: torch.Tensor, w, kw: dict, nxt, gated: bool = False, feeds_gemm: bool = False):
-        """Row-parallel projection followed by the sum over ranks. With `feeds_gemm` (the sum only feeds the next FP8
-        projection) and the library's own all-reduce, the sum and that projection's activation quantizer run as one
-        kernel and the result is the (q, scale) pair."""
-        if self.tp == 1:
-            return self._project(h, w, kw, nxt, gated=gated)
-        self.collectives += 1
-        if self.comm is None:
-            y = self._project(h, w, kw, nxt, gated=gated)
-            dist.all_reduce(y, group=self.group)
-            return y
-        idx = self._ar_index
-        self._ar_index += 1
+    def _row_parallel(self, h, w, kw: dict, nxt, resid, gated: bool = False, feeds_gemm: bool = False):
+        """Row-parallel projection, sum over ranks, residual add. Returns (input of the next projection, hidden state);
+        the former is a (q, scale) pair when a fused kernel already quantized it for an FP8 projection."""
         rows = h[0].shape[0] if isinstance(h, tuple) else h.shape[0]
-        part = self._project(h, w, kw, nxt, out=self.comm.view(idx, (rows, w.shape[0]), self.act_dtype), gated=gated)
-        if feeds_gemm and self.fuse_quant and self.kind == "fp8" and rows <= 64 and w.shape[0] % 8 == 0 and w.shape[0] <= 16384:
-            return self.comm.reduce_quantize_fp8(idx, rows, w.shape[0], self.act_dtype)
-        return self.comm.reduce(idx, torch.empty_like(part))
+        cols = w.shape[0]
+        add = resid if self.residual else None
+        if self.push:
+            idx = self._ar_index
+            self._ar_index += 1
+            self.collectives += 1 if self.tp > 1 else 0
+            self.reduces += 1
+
+            def pushed(x, wt, *, out_dtype, **kwargs):
+                self.comm.gemm_push(idx, x, wt, out_dtype=out_dtype, **kwargs)
+
+            self._project(h, w, kw, nxt, gated=gated, gemm=pushed)
+            quant = feeds_gemm and self.kind == "fp8"
+            out, q, s = self.comm.reduce_local(idx, rows, cols, self.act_dtype, residual=add,
+                                               want_out=self.residual or not quant, quantize=quant)
+            return ((q, s) if quant else out), out
+        if self.tp == 1:
+            y = self._project(h, w, kw, nxt, gated=gated)
+        else:
+            self.collectives += 1
+            if self.comm is None:
+                y = self._project(h, w, kw, nxt, gated=gated)
+                dist.all_reduce(y, group=self.group)
+            else:
+                idx = self._ar_index
+                self._ar_index += 1
+                self.reduces += 1
+                part = self._project(h, w, kw, nxt, out=self.comm.view(idx, (rows, cols), self.act_dtype), gated=gated)
+                fused = (feeds_gemm and self.fuse_quant and self.kind == "fp8" and add is None and rows <= 64
+                         and cols % 8 == 0 and cols <= 16384)
+                if fused:
+                    return self.comm.reduce_quantize_fp8(idx, rows, cols, self.act_dtype), None
+                y = self.comm.reduce(idx, torch.empty_like(part))
+        if add is not None:
+            y = y + add
+        return y, y
 
     def run(self, x: torch.Tensor) -> torch.Tensor:
         """x [M, hidden] replicated on every rank -> [M, hidden] replicated (after the last all-reduce)."""
@@ -154,16 +189,17 @@ class DecodeStep:
         order = self._order()
         nxt_w = {order[i]: self.layers[order[(i + 1) % len(order)][0]].w[order[(i + 1) % len(order)][1]][0]
                  for i in range(len(order))}
-        sh = self.shape
-        a_width = sh.hidden // self.tp
+        a_width = self.shape.hidden // self.tp
+        h_in, hidden = x, x
         for li, layer in enumerate(self.layers):
-            qkv = self._project(x, *layer.w["qkv"], nxt_w[(li, "qkv")])
+            qkv = self._project(h_in, *layer.w["qkv"], nxt_w[(li, "qkv")])
             attn = qkv[:, :a_width]  # stand-in for this rank's attention heads' output
             if attn.data_ptr() % 16 or (attn.stride(0) * attn.element_size()) % 16:
                 attn = attn.contiguous()  # the GEMM takes strided rows as long as they stay 16-byte aligned
-            o = self._row_parallel(attn, *layer.w["o"], nxt_w[(li, "o")], feeds_gemm=True)
-            gu = self._project(o, *layer.w["gate_up"], nxt_w[(li, "gate_up")])
-            # the last layer's sum is the step's result; every other one only feeds the next layer's QKV projection
-            x = self._row_parallel(gu, *layer.w["down"], nxt_w[(li, "down")], gated=True,
-                                   feeds_gemm=li + 1 < len(self.layers))
-        return x
+            o_in, hidden = self._row_parallel(attn, *layer.w["o"], nxt_w[(li, "o")], hidden, feeds_gemm=True)
+            gu = self._project(o_in, *layer.w["gate_up"], nxt_w[(li, "gate_up")])
+            # the last layer's sum is the step's result; every other one also feeds the next layer's QKV projection
+            last = li + 1 == len(self.layers)
+            h_in, hidden = self._row_parallel(gu, *layer.w["down"], nxt_w[(li, "down")], hidden, gated=True,
+                                              feeds_gemm=not last)
+        return hidden if hidden is not None else h_in

@@ -1,6 +1,7 @@
 """Multi-GPU tests (need >= 2 GPUs on the box; skipped otherwise): the one-shot peer-memory all-reduce against an
-fp32 rank-order sum, its fusion with the FP8 quantizer against the two separate kernels (bitwise), and the
-tensor-parallel decode step with it against the same step over NCCL."""
+fp32 rank-order sum, its fusion with the FP8 quantizer against the two separate kernels (bitwise), the push form
+(transfer inside the row-parallel GEMM's epilogue, residual add and quantizer in the consumer) against the pull form
+(bitwise), and the tensor-parallel decode step with the library's all-reduce against the same step over NCCL."""
 import os
 import socket
 
@@ -59,7 +60,8 @@ def _worker(rank, world, port, out_dir):
                 if keep:
                     same = same and torch.equal(out, summed)
                 res["arq"] = res["arq"] and bool(same)
-        # graph replay: flags return to zero, so the same captured launch works again and again
+        # graph replay: the signal counters only grow and every rank replays the same sequence, so a captured launch
+        # works again and again
         part = torch.randn(8, 8192, device=dev, generator=torch.Generator(device=dev).manual_seed(rank)).to(torch.bfloat16)
         buf, out = ar.view(0, (8, 8192), torch.bfloat16), torch.empty(8, 8192, device=dev, dtype=torch.bfloat16)
         buf2, out2 = ar.view(1, (8, 8192), torch.bfloat16), torch.empty(8, 8192, device=dev, dtype=torch.bfloat16)
@@ -92,6 +94,29 @@ def _worker(rank, world, port, out_dir):
         y_sep = TP.DecodeStep("fp8", 2, world, rank, dev, shape=shape, comm=ar3, fuse_quant=False).run(x)
         y_fus = TP.DecodeStep("fp8", 2, world, rank, dev, shape=shape, comm=ar3, fuse_quant=True).run(x)
         res["fp8_fused_equal"] = bool(torch.equal(y_sep, y_fus)) and bool(torch.isfinite(y_fus.float()).all())
+        # push form (GEMM epilogue stores into every rank's buffer, one consumer sums, adds the residual, quantizes)
+        # against the pull form with separate residual add and quantizer: same bits, eagerly and from a replayed graph
+        res["push_equal"] = True
+        for kind in ("fp8", "bf16"):
+            ar_pull = CM.OneShotAllReduce(None, dev, max_bytes=4 * 1024 * 2, ctas=4)
+            ar_push = CM.OneShotAllReduce(None, dev, max_bytes=4 * 1024 * 2, ctas=4)
+            y_pull = TP.DecodeStep(kind, 2, world, rank, dev, shape=shape, comm=ar_pull, residual=True, fuse_quant=False).run(x)
+            pstep = TP.DecodeStep(kind, 2, world, rank, dev, shape=shape, comm=ar_push, residual=True, push=True)
+            y_push = pstep.run(x)
+            same = bool(torch.equal(y_pull, y_push)) and bool(torch.isfinite(y_push.float()).all())
+            sg = torch.cuda.Stream()
+            sg.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(sg):
+                pgraph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(pgraph):
+                    y_cap = pstep.run(x)
+            torch.cuda.current_stream().wait_stream(sg)
+            for _ in range(3):
+                pgraph.replay()
+                torch.cuda.synchronize()
+                same = same and bool(torch.equal(y_cap, y_pull))
+            res["push_equal"] = res["push_equal"] and same
+            del pgraph
         torch.cuda.synchronize()
         denom = y_nccl.float().abs().max().clamp_min(1e-6)
         res["tp_close"] = float(((y_one.float() - y_nccl.float()).abs().max() / denom).item())
@@ -111,5 +136,5 @@ def test_oneshot_allreduce_and_tp_step(tmp_path):
         res = torch.load(tmp_path / f"r{r}.pt")
         assert all(res[f"ar{i}"] for i in range(4)), res
         assert res["replay"] and res["status"] == 0, res
-        assert res["arq"] and res["fp8_fused_equal"], res
+        assert res["arq"] and res["fp8_fused_equal"] and res["push_equal"], res
         assert res["tp_close"] < 3e-2, res  # bf16 partials are rounded before NCCL sums them, fp32 here

@@ -21,13 +21,14 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(N.SYMBOLS), declared ^ set(N.SYMBOLS)
     for name in declared:
         assert hasattr(N.lib, name)
-    assert N.lib.llg_abi_version() == 1
+    assert N.lib.llg_abi_version() == N.ABI_VERSION == int(re.search(r"#define LLG_ABI_VERSION (\d+)", header).group(1))
 
 
 def test_struct_layout_matches_library():
-    sizes = (C.c_int32 * 3)()
+    sizes = (C.c_int32 * 5)()
     N.lib.llg_struct_sizes(C.byref(sizes))
-    assert tuple(sizes) == (C.sizeof(N.SkinnyArgs), C.sizeof(N.TcArgs), C.sizeof(N.QuantArgs))
+    assert tuple(sizes) == (C.sizeof(N.SkinnyArgs), C.sizeof(N.TcArgs), C.sizeof(N.QuantArgs), C.sizeof(N.GatedQuantArgs),
+                            C.sizeof(N.PushArgs))
 
 
 def test_tc_info_table():

@@ -32,8 +32,8 @@ def full_weights():
     return out
 
 
-def build_step(tp, rank, group=None):
-    step = TP.DecodeStep("bf16", LAYERS, tp, rank, "cpu", shape=SHAPE, group=group, gemm_fn=host_gemm)
+def build_step(tp, rank, group=None, residual=False):
+    step = TP.DecodeStep("bf16", LAYERS, tp, rank, "cpu", shape=SHAPE, group=group, gemm_fn=host_gemm, residual=residual)
     for layer, full in zip(step.layers, full_weights()):
         layer.w = {"qkv": (TP.shard_rows(full["qkv"], tp, rank), {}), "o": (TP.shard_cols(full["o"], tp, rank), {}),
                    "gate_up": (TP.shard_gate_up(full["gate_up"], tp, rank), {}),
@@ -41,8 +41,9 @@ def build_step(tp, rank, group=None):
     return step
 
 
-def emulate(tp, x):
-    """The same step without processes: every rank's partial computed in turn, row-parallel outputs summed."""
+def emulate(tp, x, residual=False):
+    """The same step without processes: every rank's partial computed in turn, row-parallel outputs summed (and, with
+    `residual`, added to the hidden state that the next projection then reads)."""
     fulls = full_weights()
     x = x.double()
     for full in fulls:
@@ -50,12 +51,14 @@ def emulate(tp, x):
         for r in range(tp):
             qkv = x @ TP.shard_rows(full["qkv"], tp, r).double().T
             o += qkv[:, : SHAPE.hidden // tp] @ TP.shard_cols(full["o"], tp, r).double().T
+        if residual:
+            o = o + x
         d = torch.zeros(M, SHAPE.hidden, dtype=torch.float64)
         for r in range(tp):
             gu = o @ TP.shard_gate_up(full["gate_up"], tp, r).double().T
             half = gu.shape[1] // 2
             d += (torch.nn.functional.silu(gu[:, :half]) * gu[:, half:]) @ TP.shard_cols(full["down"], tp, r).double().T
-        x = d
+        x = d + o if residual else d
     return x
 
 
@@ -66,7 +69,8 @@ def _rank_main(rank, world, port, out):
         x = torch.randn(M, SHAPE.hidden, generator=torch.Generator().manual_seed(7))
         step = build_step(world, rank)
         y = step.run(x)
-        torch.save({"y": y, "collectives": step.collectives, "gemms": step.gemms}, f"{out}/rank{rank}.pt")
+        y_res = build_step(world, rank, residual=True).run(x.double())
+        torch.save({"y": y, "y_res": y_res, "collectives": step.collectives, "gemms": step.gemms}, f"{out}/rank{rank}.pt")
     finally:
         dist.destroy_process_group()
 
@@ -94,6 +98,8 @@ def test_single_rank_step_equals_emulation():
     y = step.run(x)
     assert step.collectives == 0 and step.gemms == 4 * LAYERS
     assert torch.allclose(y, emulate(1, x), rtol=1e-12, atol=1e-12)
+    y_res = build_step(1, 0, residual=True).run(x.double())
+    assert torch.allclose(y_res, emulate(1, x, residual=True), rtol=1e-12, atol=1e-12)
 
 
 def test_two_gloo_ranks_match_emulation(tmp_path):
@@ -107,6 +113,7 @@ def test_two_gloo_ranks_match_emulation(tmp_path):
     for g in got:
         assert g["collectives"] == 2 * LAYERS and g["gemms"] == 4 * LAYERS
         assert torch.allclose(g["y"], want, rtol=1e-11, atol=1e-11)
+        assert torch.allclose(g["y_res"], emulate(2, x, residual=True), rtol=1e-11, atol=1e-11)
     assert torch.equal(got[0]["y"], got[1]["y"])  # replicated after the last all-reduce
     # and TP2 computes the same function as a differently-sharded TP1 up to the head stand-in: only check finiteness there
     assert np.isfinite(want.numpy()).all()
