@@ -263,9 +263,8 @@ __global__ void __launch_bounds__(kArqThreads) reduce_local_kernel(const RlDev p
   if (tid < p.world) {
     if (!flag_recv(p.flags + (int64_t)row * p.world + tid, p.flags + ((int64_t)LLG_AR_MAX_CTAS + row) * p.world + tid, p.spin))
       atomicCAS(p.status, 0u, (unsigned)ST_ALLREDUCE_WAIT);
-    __threadfence_system();
   }
-  __syncthreads();
+  __syncthreads();  // the waiters' acquire loads, then this barrier: every thread may now read the partials
   const int units = p.cols >> 3;
   float r[kArqUnits][8];
   float a = 0.f;
