@@ -25,6 +25,12 @@ def _args(x, w, kw, y, ws, cnt, ksplit, kind_id=2, cfg=0):
                              kw["x_scale"].float().contiguous(), None, None, 1.0, kind_id, True, True, cfg, 4, ksplit, ws, cnt)
 
 
+def _bare(a):
+    """The same call without workspace and counters: the variant must not need them."""
+    a.ws, a.ws_elems, a.counters, a.counters_elems = None, 0, None, 0
+    return a
+
+
 def test_static_workspace_entry_matches_regular_entry_twice():
     dev = torch.device("cuda", torch.cuda.current_device())
     stream = torch.cuda.current_stream().cuda_stream
@@ -33,14 +39,17 @@ def test_static_workspace_entry_matches_regular_entry_twice():
         ws, cnt = L._workspace(dev, ksplit * n * m, 64)
         want = torch.empty(m, n, device=dev, dtype=torch.float32)
         N.check(N.lib.llg_tc_gemm(C.byref(_args(x, w, kw, want, ws, cnt, ksplit)), stream))
-        empty = torch.empty(0, device=dev)
-        for call in range(2):
-            got = torch.full((m, n), float("nan"), device=dev, dtype=torch.float32)
-            a = _args(x, w, kw, got, ws, cnt, ksplit)
-            a.ws, a.ws_elems, a.counters, a.counters_elems = None, 0, None, 0  # the variant must not need them
+        outs = [torch.full((m, n), float("nan"), device=dev, dtype=torch.float32) for _ in range(2)]
+        N.check(N.lib.llg_tc_gemm_static_ws(C.byref(_bare(_args(x, w, kw, torch.empty_like(want), ws, cnt, ksplit))), stream))
+        calls = [_bare(_args(x, w, kw, outs[call], ws, cnt, ksplit)) for call in range(2)]  # descriptors built beforehand
+        torch.cuda.synchronize()  # the first call on the device has looked the scratch address up; from here on ...
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        for a in calls:
             N.check(N.lib.llg_tc_gemm_static_ws(C.byref(a), stream))
-            torch.cuda.synchronize()
-            assert torch.equal(got, want), (m, n, k, ksplit, call)  # same kernel, same summation order: same bits
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free_before  # ... a call takes no device memory from anyone
+        for call in range(2):
+            assert torch.equal(outs[call], want), (m, n, k, ksplit, call)  # same kernel, same summation order: same bits
     assert N.device_status() == 0
 
 
