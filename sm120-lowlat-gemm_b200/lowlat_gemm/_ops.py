@@ -1,9 +1,15 @@
 """torch.ops.lowlat_gemm.*: the custom-op boundary, with the schema strings of the reference's TORCH_LIBRARY block
 (csrc/ops.cpp:420-440) so callers written against it (tests, tools, serving hooks) work unchanged.
 
-Each op checks what only a tensor knows (device, dtype, contiguity; reference csrc/ops.cpp:26-28, 63-83, 170-199,
-308-360), then hands raw pointers, sizes and strides to libllg_core, which validates the rest and launches on the
-current CUDA stream of the operand's device. Errors surface as RuntimeError("lowlat_gemm: ...").
+Two registrations of the same seven ops exist, both thin layers over the C ABI of libllg_core:
+  * the C++ torch extension lowlat_gemm._C (csrc/ops.cpp, the counterpart of the reference's extension module): used
+    whenever it has been built;
+  * this module's torch.library registration over ctypes: the torch-free binding's sibling, used when _C is absent or
+    when LLG_OPS=ctypes asks for it.
+BACKEND says which one is active. Each op checks what only a tensor knows (device, dtype, contiguity; reference
+csrc/ops.cpp:26-28, 63-83, 170-199, 308-360), then hands raw pointers, sizes and strides to libllg_core, which
+validates the rest and launches on the current CUDA stream of the operand's device. Errors surface as
+RuntimeError("lowlat_gemm: ...").
 """
 
 from __future__ import annotations
@@ -16,22 +22,36 @@ from . import _native as N
 
 _DT = {torch.bfloat16: 1, torch.float16: 2, torch.float32: 3}
 
-_lib = torch.library.Library("lowlat_gemm", "DEF")
-_lib.define("skinny(Tensor x, Tensor w, Tensor ws, Tensor counters, int rows, int unroll, int lanes_per_row, "
-            "int warps, int ksplit, bool out_fp32=False, bool cluster=False, Tensor? prefetch=None, "
-            "int prefetch_bytes=0) -> Tensor")
-_lib.define("skinny_out(Tensor(a!) y, Tensor x, Tensor w, Tensor ws, Tensor counters, int rows, int unroll, "
-            "int lanes_per_row, int warps, int ksplit, bool cluster=False, Tensor? prefetch=None, "
-            "int prefetch_bytes=0) -> ()")
-_lib.define("tc_gemm(Tensor(a!) y, Tensor a, Tensor b, Tensor? a_sf, Tensor? b_sf, Tensor? row_scale, "
-            "Tensor? col_scale, Tensor? bias, Tensor? alpha_t, float alpha, int kind, bool swap, bool bias_on_p, "
-            "int cfg, int stages, int ksplit, Tensor ws, Tensor counters, bool cluster=False, Tensor? prefetch=None, "
-            "int prefetch_bytes=0) -> ()")
-_lib.define("quant(Tensor x, Tensor(a!) q, Tensor(b!)? sf, Tensor? scale_in, Tensor(c!)? scale_out, int mode, "
-            "float min_scale) -> ()")
-_lib.define("tc_info(int kind, int cfg) -> int[]")
-_lib.define("set_pdl(bool on) -> ()")
-_lib.define("pdl_enabled() -> bool")
+def _try_cpp() -> bool:
+    import os
+
+    if os.environ.get("LLG_OPS", "").lower() == "ctypes":
+        return False
+    try:
+        from . import _C  # noqa: F401  (its import registers the ops)
+    except ImportError:
+        return False
+    return True
+
+
+BACKEND = "cpp" if _try_cpp() else "ctypes"
+_lib = torch.library.Library("lowlat_gemm", "DEF" if BACKEND == "ctypes" else "FRAGMENT")
+if BACKEND == "ctypes":
+    _lib.define("skinny(Tensor x, Tensor w, Tensor ws, Tensor counters, int rows, int unroll, int lanes_per_row, "
+                "int warps, int ksplit, bool out_fp32=False, bool cluster=False, Tensor? prefetch=None, "
+                "int prefetch_bytes=0) -> Tensor")
+    _lib.define("skinny_out(Tensor(a!) y, Tensor x, Tensor w, Tensor ws, Tensor counters, int rows, int unroll, "
+                "int lanes_per_row, int warps, int ksplit, bool cluster=False, Tensor? prefetch=None, "
+                "int prefetch_bytes=0) -> ()")
+    _lib.define("tc_gemm(Tensor(a!) y, Tensor a, Tensor b, Tensor? a_sf, Tensor? b_sf, Tensor? row_scale, "
+                "Tensor? col_scale, Tensor? bias, Tensor? alpha_t, float alpha, int kind, bool swap, bool bias_on_p, "
+                "int cfg, int stages, int ksplit, Tensor ws, Tensor counters, bool cluster=False, Tensor? prefetch=None, "
+                "int prefetch_bytes=0) -> ()")
+    _lib.define("quant(Tensor x, Tensor(a!) q, Tensor(b!)? sf, Tensor? scale_in, Tensor(c!)? scale_out, int mode, "
+                "float min_scale) -> ()")
+    _lib.define("tc_info(int kind, int cfg) -> int[]")
+    _lib.define("set_pdl(bool on) -> ()")
+    _lib.define("pdl_enabled() -> bool")
 
 
 def _need(cond: bool, msg: str) -> None:
@@ -237,11 +257,12 @@ def _pdl_enabled():
     return bool(N.lib.llg_pdl_enabled())
 
 
-_lib.impl("skinny", _skinny, "CUDA")
-_lib.impl("skinny", _skinny_meta, "Meta")
-_lib.impl("skinny_out", _skinny_out, "CUDA")
-_lib.impl("tc_gemm", _tc_gemm, "CUDA")
-_lib.impl("quant", _quant, "CUDA")
-_lib.impl("tc_info", _tc_info, "CompositeExplicitAutograd")
-_lib.impl("set_pdl", _set_pdl, "CompositeExplicitAutograd")
-_lib.impl("pdl_enabled", _pdl_enabled, "CompositeExplicitAutograd")
+if BACKEND == "ctypes":
+    _lib.impl("skinny", _skinny, "CUDA")
+    _lib.impl("skinny", _skinny_meta, "Meta")
+    _lib.impl("skinny_out", _skinny_out, "CUDA")
+    _lib.impl("tc_gemm", _tc_gemm, "CUDA")
+    _lib.impl("quant", _quant, "CUDA")
+    _lib.impl("tc_info", _tc_info, "CompositeExplicitAutograd")
+    _lib.impl("set_pdl", _set_pdl, "CompositeExplicitAutograd")
+    _lib.impl("pdl_enabled", _pdl_enabled, "CompositeExplicitAutograd")

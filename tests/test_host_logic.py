@@ -165,3 +165,24 @@ def test_missing_library_fails_loudly(tmp_path):
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
                        env={"LLG_CORE_LIB": str(tmp_path / "nope.so"), "PATH": "/usr/bin"})
     assert r.returncode != 0 and "there is no fallback implementation" in r.stderr
+
+
+def test_cpp_extension_registers_the_reference_schemas():
+    """With lowlat_gemm._C built, the ops come from the C++ extension; either way the seven schemas are the reference's
+    (csrc/ops.cpp:420-440), and the ctypes registration can still be asked for in a fresh interpreter."""
+    from lowlat_gemm import _ops
+    built = any((ROOT / "sm120-lowlat-gemm_b200" / "lowlat_gemm").glob("_C*.so"))
+    assert _ops.BACKEND == ("cpp" if built else "ctypes")
+    ns = torch.ops.lowlat_gemm
+    assert str(ns.tc_info.default._schema) == "lowlat_gemm::tc_info(int kind, int cfg) -> int[]"
+    assert "bool out_fp32=False, bool cluster=False, Tensor? prefetch=None, int prefetch_bytes=0) -> Tensor" in str(ns.skinny.default._schema)
+    assert "Tensor(a!) y, Tensor a, Tensor b, Tensor? a_sf, Tensor? b_sf, Tensor? row_scale" in str(ns.tc_gemm.default._schema)
+    assert "Tensor(a!) q, Tensor(b!)? sf, Tensor? scale_in, Tensor(c!)? scale_out, int mode, float min_scale" in str(ns.quant.default._schema)
+    assert list(ns.tc_info(0, 0)) == list(N.tc_info(0, 0)) and ns.pdl_enabled() in (True, False)
+    y = ns.skinny(torch.empty(3, 64, dtype=torch.bfloat16, device="meta"), torch.empty(7, 64, dtype=torch.bfloat16, device="meta"),
+                  torch.empty(0, device="meta"), torch.empty(0, device="meta"), 1, 4, 32, 4, 1, True)
+    assert tuple(y.shape) == (3, 7) and y.dtype == torch.float32
+    code = "import sys; sys.path.insert(0, %r); from lowlat_gemm import _ops; print(_ops.BACKEND)" % str(ROOT / "sm120-lowlat-gemm_b200")
+    import os
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=dict(os.environ, LLG_OPS="ctypes"), check=True)
+    assert r.stdout.strip().splitlines()[-1] == "ctypes"
