@@ -211,8 +211,8 @@ LLG_API int llg_allreduce_quant_fp8(const void* const* buffers_dev, uint32_t* co
  * sent one way. The consumer on every rank is llg_reduce_local. `done` is a zero-initialised counter local to this
  * rank that the kernel returns to zero. rows = the GEMM's token count (<= LLG_AR_MAX_CTAS); world <= 8. Consecutive
  * pushes must alternate between two destination buffers, as with llg_allreduce_oneshot. No multicast, no TMA on peer
- * memory. No counterpart in the reference (it has no multi-GPU code); SURVEY-level analogue: the row-parallel
- * projections of tools/decode_step.py:27-40 followed by the framework's all-reduce. */
+ * memory. No counterpart in the reference (it has no multi-GPU code); nearest analogue: the row-parallel projections
+ * in the op sequence of tools/decode_step.py:27-40, followed by the framework's all-reduce. */
 typedef struct llg_push_args {
   int32_t world, rank, rows, reserved;
   void* dst[8];

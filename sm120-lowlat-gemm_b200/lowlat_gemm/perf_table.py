@@ -3,7 +3,7 @@
     python -m lowlat_gemm.perf_table [--configs c1,c2,c3,c4] [--plans plans.json] [--pdl] [--json out.json]
 
 Cold-weight CUDA-graph timing (lowlat_gemm/timing.py). Bandwidth = algorithmic bytes of the GEMM (every operand touched
-once) / time, reported against the nominal 8 TB/s and against a measured copy bandwidth (--measured-gbs). The
+once) / time, reported against the nominal 8 TB/s and against a measured copy bandwidth when --measured-gbs gives one. The
 counterpart of the reference's tools/bench.py:44-85.
 """
 
@@ -41,7 +41,7 @@ def main() -> None:
     ap.add_argument("--pdl", action="store_true")
     ap.add_argument("--prefetch-next", action="store_true")
     ap.add_argument("--prefetch-mb", type=float, default=16)
-    ap.add_argument("--measured-gbs", type=float, default=6537.6)
+    ap.add_argument("--measured-gbs", type=float, default=0.0, help="measured copy bandwidth of this GPU in GB/s; 0 leaves that column out")
     ap.add_argument("--json")
     ap.add_argument("--replays", type=int, default=20)
     args = ap.parse_args()
@@ -74,11 +74,11 @@ def main() -> None:
                 if plan.skinny is not None and m <= min(plan.skinny_max_m, 16):
                     desc = f"skinny lanes={plan.skinny.lanes_per_row} ks={plan.skinny.ksplit} {plan.skinny.tile(m)}"
                 else:
-                    ch = L._tc_lookup(plan.tc, m) or L.default_tc_choice(kind, m, n, k, 148)
+                    ch = L._tc_lookup(plan.tc, m) or L.default_tc_choice(kind, m, n, k, torch.cuda.get_device_properties(dev).multi_processor_count)
                     desc = f"cfg{ch.cfg} swap={int(ch.swap)} st={ch.stages} ks={ch.ksplit}{' cl' if ch.cluster else ''}"
-                print(f"{kind:11s} {n:6d} {k:5d} {m:4d} {us:8.2f} {gbs:8.0f} {gbs / 80:7.1f} {100 * gbs / args.measured_gbs:6.1f}  {desc}", flush=True)
+                print(f"{kind:11s} {n:6d} {k:5d} {m:4d} {us:8.2f} {gbs:8.0f} {gbs / 80:7.1f} {(100 * gbs / args.measured_gbs) if args.measured_gbs else float('nan'):6.1f}  {desc}", flush=True)
                 rows.append({"config": cname, "kind": kind, "n": n, "k": k, "m": m, "us": us, "bytes": nbytes, "gbs": gbs,
-                             "pct_8tbs": gbs / 80, "pct_measured": 100 * gbs / args.measured_gbs, "plan": desc})
+                             "pct_8tbs": gbs / 80, "pct_measured": (100 * gbs / args.measured_gbs) if args.measured_gbs else None, "plan": desc})
             del cold
             torch.cuda.empty_cache()
     if args.json:

@@ -9,6 +9,7 @@ one or two 128-byte K atoms per pipeline stage) and the shared-memory budget is 
 
 from __future__ import annotations
 
+import bisect
 import json
 import os
 import threading
@@ -128,23 +129,29 @@ class Plan:
                    prefer_vendor=[int(m) for m in d.get("prefer_vendor", [])])
 
 
-def _tc_lookup(table: dict, m: int):
-    """Tuned entry for m: that of the largest tuned M <= m; no answer beyond twice the largest tuned M."""
-    if m in table:
-        return table[m]
-    if not table or m > 2 * max(table):
+def _floor_entry(table: dict, m: int):
+    """(largest key <= m, its value), falling back to the smallest key when every key is larger; None for an empty
+    table. The rule both lookups share: an entry tuned for M tokens also serves the token counts above it."""
+    if not table:
         return None
-    below = [t for t in table if t <= m]
-    return table[max(below)] if below else table[min(table)]
+    keys = sorted(table)
+    at = bisect.bisect_right(keys, m)
+    key = keys[at - 1] if at else keys[0]
+    return key, table[key]
+
+
+def _tc_lookup(table: dict, m: int):
+    """Tuned tensor-core entry for m tokens: that of the largest tuned M <= m, but no answer at all beyond twice the
+    largest tuned M - there the heuristics decide (reference lowlat_gemm/__init__.py:177-184)."""
+    hit = _floor_entry(table, m)
+    if hit is None or m > 2 * max(table):
+        return None
+    return hit[1]
 
 
 def _nearest(table: dict, m: int, default):
-    if m in table:
-        return table[m]
-    below = [t for t in table if t <= m]
-    if below:
-        return table[max(below)]
-    return table[min(table)] if table else default
+    hit = _floor_entry(table, m)
+    return default if hit is None else hit[1]
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -256,38 +263,30 @@ def default_tc_choice(kind: str, m: int, n: int, k: int, sm_count: int) -> TcCho
     return TcChoice(cfg=cfg, swap=swap, stages=stages, ksplit=best, cluster=best > 1)
 
 
+_HEURISTIC_TOKENS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 1024, 4096)
+
+
 def default_plan(kind: str, n: int, k: int, sm_count: int) -> Plan:
-    plan = Plan()
-    if kind in ("bf16", "f16"):
-        plan.skinny = default_skinny_order(n, k, sm_count)
-        plan.skinny_max_m = 1
-    for m in (1, 2, 4, 8, 16, 32, 64, 128, 256, 1024, 4096):
-        plan.tc[m] = default_tc_choice(kind, m, n, k, sm_count)
-    return plan
+    """Plan from heuristics alone: a tensor-core choice per power-of-two token count and, for W16A16, the skinny engine
+    for the single-token call (the only one where it matches the tensor cores on B200)."""
+    w16 = kind in ("bf16", "f16")
+    return Plan(skinny=default_skinny_order(n, k, sm_count) if w16 else None, skinny_max_m=1 if w16 else 0,
+                tc={m: default_tc_choice(kind, m, n, k, sm_count) for m in _HEURISTIC_TOKENS})
 
 
 # ---------------------------------------------------------------------------------------------------------------
-# registry
-
-_lock = threading.Lock()
-_plans: dict[tuple[str, str, int, int], Plan] = {}
-_loaded: set[str] = set()
-_sm_counts: dict[int, int] = {}
+# registry: plans per device name. Sources in rising priority: heuristics, the packaged plans/<device>.json, the file
+# named by LLG_PLAN_FILE, load_plans(), set_plan() (reference lowlat_gemm/__init__.py:265-349).
 
 
 def _dev(device: torch.device | None) -> torch.device:
-    if device is None or device.index is None:
-        return torch.device("cuda", torch.cuda.current_device())
-    return device
-
-
-def _sm_count(device: torch.device) -> int:
-    if device.index not in _sm_counts:
-        _sm_counts[device.index] = torch.cuda.get_device_properties(device.index).multi_processor_count
-    return _sm_counts[device.index]
+    if device is not None and device.index is not None:
+        return device
+    return torch.device("cuda", torch.cuda.current_device())
 
 
 def _file_key(name: str) -> str:
+    """Device name -> file stem: lower case, every run of other characters an underscore ("NVIDIA B200" -> nvidia_b200)."""
     return "".join(ch if ch.isalnum() else "_" for ch in name).strip("_").lower()
 
 
@@ -295,30 +294,68 @@ def _packaged_path(name: str) -> Path:
     return Path(__file__).with_name("plans") / f"{_file_key(name)}.json"
 
 
-def _ingest(data: dict, name: str) -> int:
-    entries = data.get("plans", {})
-    with _lock:
-        for key, d in entries.items():
-            kind, shape = key.split(":")
-            n, k = (int(v) for v in shape.lower().split("x"))
-            _plans[(name, kind, n, k)] = Plan.from_json(d)
-    return len(entries)
+def _parse_key(key: str) -> tuple[str, int, int]:
+    kind, shape = key.split(":")
+    n, k = shape.lower().split("x")
+    return kind, int(n), int(k)
 
 
-def _ensure_loaded(name: str) -> None:
-    if name in _loaded:
-        return
-    with _lock:
-        if name in _loaded:
-            return
-        _loaded.add(name)
-    packaged = _packaged_path(name)
-    if packaged.is_file():
-        _ingest(json.loads(packaged.read_text()), name)
-    env = os.environ.get("LLG_PLAN_FILE")
-    if env:
-        data = json.loads(Path(env).read_text())
-        _ingest(data, data.get("device") or name)
+class _PlanStore:
+    """All plans of the process, keyed by (device name, kind, N, K), behind one lock."""
+
+    def __init__(self):
+        self._lock = threading.Lock()
+        self._plans: dict[tuple[str, str, int, int], Plan] = {}
+        self._seeded: set[str] = set()      # device names whose packaged / environment plans have been read
+        self._sms: dict[int, int] = {}
+
+    def sm_count(self, device: torch.device) -> int:
+        if device.index not in self._sms:
+            self._sms[device.index] = torch.cuda.get_device_properties(device.index).multi_processor_count
+        return self._sms[device.index]
+
+    def ingest(self, data: dict, name: str) -> int:
+        parsed = {_parse_key(key): Plan.from_json(body) for key, body in data.get("plans", {}).items()}
+        with self._lock:
+            for (kind, n, k), plan in parsed.items():
+                self._plans[(name, kind, n, k)] = plan
+        return len(parsed)
+
+    def seed(self, name: str) -> None:
+        """First use of a device name: read its packaged plans, then the file LLG_PLAN_FILE names (which wins)."""
+        with self._lock:
+            if name in self._seeded:
+                return
+            self._seeded.add(name)
+        packaged = _packaged_path(name)
+        if packaged.is_file():
+            self.ingest(json.loads(packaged.read_text()), name)
+        extra = os.environ.get("LLG_PLAN_FILE")
+        if extra:
+            data = json.loads(Path(extra).read_text())
+            self.ingest(data, data.get("device") or name)
+
+    def put(self, name: str, kind: str, n: int, k: int, plan: Plan) -> None:
+        self.seed(name)
+        with self._lock:
+            self._plans[(name, kind, n, k)] = plan
+
+    def get(self, name: str, kind: str, n: int, k: int, sm_count: int) -> Plan:
+        self.seed(name)
+        key = (name, kind, n, k)
+        plan = self._plans.get(key)
+        if plan is None:
+            fresh = default_plan(kind, n, k, sm_count)  # computed outside the lock: it queries the library
+            with self._lock:
+                plan = self._plans.setdefault(key, fresh)
+        return plan
+
+
+_store = _PlanStore()
+
+
+def _sm_count(device: torch.device) -> int:
+    return _store.sm_count(device)
 
 
 def load_plans(path: str | os.PathLike, device_name: str | None = None) -> int:
@@ -327,8 +364,8 @@ def load_plans(path: str | os.PathLike, device_name: str | None = None) -> int:
     name = device_name or data.get("device")
     if not name:
         raise ValueError(f"{path}: no device name in the file and none given")
-    _ensure_loaded(name)
-    return _ingest(data, name)
+    _store.seed(name)
+    return _store.ingest(data, name)
 
 
 def save_plans(path: str | os.PathLike, plans: dict[tuple[str, int, int], Plan], device_name: str) -> None:
@@ -337,30 +374,19 @@ def save_plans(path: str | os.PathLike, plans: dict[tuple[str, int, int], Plan],
 
 
 def set_plan(kind: str, n: int, k: int, plan: Plan, device: torch.device | None = None) -> None:
-    name = torch.cuda.get_device_name(_dev(device))
-    _ensure_loaded(name)
-    with _lock:
-        _plans[(name, kind, n, k)] = plan
+    _store.put(torch.cuda.get_device_name(_dev(device)), kind, n, k, plan)
 
 
 def get_plan(kind: str, n: int, k: int, device: torch.device | None = None) -> Plan:
     device = _dev(device)
-    name = torch.cuda.get_device_name(device)
-    _ensure_loaded(name)
-    plan = _plans.get((name, kind, n, k))
-    if plan is None:
-        fresh = default_plan(kind, n, k, _sm_count(device))
-        with _lock:
-            plan = _plans.setdefault((name, kind, n, k), fresh)
-    return plan
+    return _store.get(torch.cuda.get_device_name(device), kind, n, k, _store.sm_count(device))
 
 
 def prefer_lowlat(kind: str, n: int, k: int, m: int, device: torch.device | None = None) -> bool:
-    """False when the plan recorded the vendor library as faster at the nearest tuned M (<= m, within 2x)."""
+    """False when the plan recorded the vendor library as faster at the tuned token count that serves m (the largest
+    tuned M <= m, within twice the largest tuned M); True whenever nothing was recorded for m."""
     plan = get_plan(kind, n, k, device)
-    if not plan.prefer_vendor or not plan.tc:
+    if not plan.prefer_vendor or _tc_lookup(plan.tc, m) is None:
         return True
-    tuned = [t for t in plan.tc if t <= m]
-    if not tuned or m > 2 * max(plan.tc):
-        return True
-    return max(tuned) not in plan.prefer_vendor
+    served_by = _floor_entry(plan.tc, m)[0]
+    return served_by > m or served_by not in plan.prefer_vendor

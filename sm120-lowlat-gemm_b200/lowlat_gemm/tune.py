@@ -1,121 +1,182 @@
 """Measure plans for a shape list and write a plan file (load it with LLG_PLAN_FILE or lowlat_gemm.load_plans, or
 install it as lowlat_gemm/plans/<device>.json).
 
-    python -m lowlat_gemm.tune --shapes shapes.json --kinds bf16,fp8 --out plans.json [--tokens 1,2,4,8,16,64]
+    python -m lowlat_gemm.tune --shapes shapes.json --kinds bf16,fp8 --out plans.json [--tokens 1,2,4,8,16,64] [--pdl]
 
-Same procedure as the reference's tuner (tools/tune.py:32-134): every tensor-core candidate (config, orientation,
-stages, K split, cluster) is timed per token count over cold weights and the fastest kept; for W16A16 the skinny
-summation order (lanes per row, K split) is chosen once per (N, K) - results stay bit-identical across token counts -
-with a tile per token count, and skinny serves the token counts where it beats the tensor-core choice, up to the first
-one where it does not. The plan file is rewritten after every shape, so an interrupted run resumes from its --out.
-The candidate grid is the B200 one: 128-row tiles, up to 16 stages of 227 KB shared memory, two CTAs per SM.
+What it does is what the reference's tuner does (tools/tune.py:32-134): per (precision, N, K) and token count, time every
+candidate over cold weights and keep the fastest; for W16A16 also pick one skinny summation order per (N, K) - results
+must stay bit-identical across token counts - with a tile per token count, and let the skinny engine serve the token
+counts, from one upwards, for which it beats the tensor-core choice. The plan file is rewritten after every shape, so
+an interrupted run resumes from its --out.
+
+How it is organised here: a `Workbench` owns the cold weights of one (kind, N, K) and times one plan at one token
+count; `tc_space()` and `skinny_space()` enumerate the B200 search spaces (128-row tcgen05 tiles with one or two K
+atoms per stage, rings up to 227 KB, cluster or workspace split-K; persistent skinny CTAs of 8 or 16 warps);
+`search()` walks them. On B200 the skinny engine only competes at one or two tokens, so its space is searched up to
+--skinny-tokens (default 2).
 """
 
 from __future__ import annotations
 
 import argparse
-import itertools
 import json
 import os
+from dataclasses import dataclass
 
 import torch
 
 import lowlat_gemm as L
 from lowlat_gemm import Plan, SkinnyOrder, SkinnyTile, TcChoice, timing
 
-SKINNY_TILES = [SkinnyTile(r, u, w) for (r, u), w in itertools.product([(1, 4), (1, 8), (2, 2), (2, 4), (4, 2)], (4, 8))]
 KSPLITS = (1, 2, 3, 4, 5, 6, 8, 10, 12, 16)
 
 
-def tc_candidates(kind: str, m: int, n: int, k: int, sm_count: int, quick: bool = False):
+@dataclass
+class Workbench:
+    """Cold weights of one (kind, N, K) and a stopwatch for plans on them."""
+
+    kind: str
+    n: int
+    k: int
+    dev: torch.device
+    replays: int = 7
+    max_calls: int = 0
+    prefetch_bytes: int = 0
+
+    def __post_init__(self):
+        self.cold = timing.ColdWeights(self.kind, self.n, self.k, self.dev)
+        self.calls = max(len(self.cold), 32)
+        if self.max_calls:
+            self.calls = min(self.calls, self.max_calls)
+        self.out_dtype = torch.float16 if self.kind == "f16" or self.kind.endswith("_f16") else torch.bfloat16
+        self._inputs: dict[int, tuple] = {}
+
+    def inputs(self, m: int):
+        if m not in self._inputs:
+            x, x_kw = timing.make_input(self.kind, m, self.k, self.dev)
+            self._inputs[m] = (x, x_kw, torch.empty(m, self.n, device=self.dev, dtype=self.out_dtype))
+        return self._inputs[m]
+
+    def microseconds(self, m: int, plan: Plan, with_scales: bool = True) -> float | None:
+        """Per-call time of gemm() under `plan`, or None when the library refuses the configuration."""
+        x, x_kw, out = self.inputs(m)
+
+        def call(w, kw, nxt):
+            extra = {"prefetch": nxt, "prefetch_bytes": self.prefetch_bytes} if self.prefetch_bytes else {}
+            scales = {**kw, **x_kw} if with_scales else {}
+            return L.gemm(x, w, out=out, plan=plan, **scales, **extra)
+
+        try:
+            return timing.time_per_call(call, self.cold, calls=self.calls, replays=self.replays)
+        except RuntimeError:
+            return None
+
+    def close(self):
+        del self.cold
+        self._inputs.clear()
+        torch.cuda.empty_cache()
+
+
+def tc_space(kind: str, m: int, n: int, k: int, sm_count: int, quick: bool = False):
+    """Tensor-core candidates worth timing for this problem on a GPU with sm_count SMs."""
+    mixed = kind in L._MIXED
     for cfg in range(L.NUM_CFGS):
-        top = L.max_stages(kind, cfg)
-        if top < 2:
+        deepest = L.max_stages(kind, cfg)
+        if deepest < 2:
             continue
-        bp, bq, _, stage = L.tc_info(kind, cfg)
-        nk = -(-k // (L.KINDS[kind][1] * L.cfg_atoms(cfg)))
-        for swap in ((True,) if kind in L._MIXED else (True, False)):
+        bp, bq, _, stage_bytes = L.tc_info(kind, cfg)
+        k_tiles = -(-k // (L.KINDS[kind][1] * L.cfg_atoms(cfg)))
+        for swap in ((True,) if mixed else (True, False)):
             p, q = (n, m) if swap else (m, n)
-            if (bq > 2 * q and bq > 16) or (not swap and p < 64):  # tile far wider than the problem
-                continue
+            if (bq > 2 * q and bq > 16) or (not swap and p < 64):
+                continue  # a tile far wider than the problem, or a handful of token rows on the 128-row side
             tiles = -(-p // bp) * -(-q // bq)
-            two_per_sm = max(2, min(top, ((L.smem_budget() - 4096) // 2) // stage))
-            for stages in sorted({min(4, top), two_per_sm, top} if quick else {min(3, top), min(4, top), two_per_sm, min(8, top), top}):
+            co_resident = max(2, min(deepest, ((L.smem_budget() - 4096) // 2) // stage_bytes))  # two CTAs per SM
+            depths = {min(4, deepest), co_resident, deepest}
+            if not quick:
+                depths |= {min(3, deepest), min(8, deepest)}
+            for stages in sorted(depths):
                 for ks in KSPLITS:
-                    if ks > 1 and (nk // ks < 2 or tiles * ks > 6 * sm_count):
+                    if ks > 1 and (k_tiles // ks < 2 or tiles * ks > 6 * sm_count):
                         continue
-                    if ks == 1 and tiles * 8 < sm_count and nk >= 8:  # a handful of CTAs cannot stream at HBM rate
-                        continue
+                    if ks == 1 and tiles * 8 < sm_count and k_tiles >= 8:
+                        continue  # a few CTAs cannot stream a long K at the HBM rate
                     yield TcChoice(cfg=cfg, swap=swap, stages=stages, ksplit=ks)
                     if 1 < ks <= 8 and not quick:
                         yield TcChoice(cfg=cfg, swap=swap, stages=stages, ksplit=ks, cluster=True)
 
 
-def tune_shape(kind: str, n: int, k: int, tokens, dev, replays: int = 7, max_calls: int = 0, quick: bool = False,
-               log=print, prefetch_bytes: int = 0) -> Plan:
+def skinny_space(k: int, quick: bool = False):
+    """(lanes per row, K split, cluster) orders and the tiles to try under each."""
+    kv = k // 8
+    tiles = [SkinnyTile(2, 4, 4), SkinnyTile(2, 4, 8), SkinnyTile(4, 2, 4), SkinnyTile(1, 4, 4)]
+    if not quick:
+        tiles += [SkinnyTile(4, 2, 8), SkinnyTile(1, 8, 4), SkinnyTile(2, 2, 4)]
+    for lanes in (32, 16, 8):
+        for ks in (1, 2, 4, 8):
+            if ks > 1 and kv // ks < 2 * lanes:
+                continue
+            for cluster in ((False,) if ks == 1 else (True,) if quick else (True, False)):
+                yield lanes, ks, cluster, tiles
+
+
+def search(kind: str, n: int, k: int, tokens, dev, replays: int = 7, max_calls: int = 0, quick: bool = False, log=print,
+           prefetch_bytes: int = 0, skinny_tokens: int = 2) -> Plan:
     sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
-    cold = timing.ColdWeights(kind, n, k, dev)
-    calls = min(max(len(cold), 32), max_calls) if max_calls else max(len(cold), 32)
-    plan = Plan()
-    tc_us = {}
-    out_dt = torch.float16 if kind == "f16" or kind.endswith("_f16") else torch.bfloat16
+    bench = Workbench(kind, n, k, dev, replays, max_calls, prefetch_bytes)
+    plan, tc_time = Plan(), {}
     for m in tokens:
-        x, x_kw = timing.make_input(kind, m, k, dev)
-        out = torch.empty(m, n, device=dev, dtype=out_dt)
-        best = None
-        for c in tc_candidates(kind, m, n, k, sm_count, quick):
-            try:
-                pf = (lambda nxt: {"prefetch": nxt, "prefetch_bytes": prefetch_bytes}) if prefetch_bytes else (lambda nxt: {})
-                t = timing.time_per_call(lambda w, kw, nxt: L.gemm(x, w, out=out, plan=Plan(tc={m: c}), **kw, **x_kw, **pf(nxt)),
-                                         cold, calls=calls, replays=replays)
-            except RuntimeError:
-                continue
-            if best is None or t < best[0]:
-                best = (t, c)
-        tc_us[m], plan.tc[m] = best
-        log(f"  {kind} {n}x{k} M={m}: {best[0]:.2f} us  {best[1]}")
-    if kind in ("bf16", "f16"):
-        skinny_ms = [m for m in tokens if m <= L.SKINNY_MAX_TOKENS]
-        kv = k // 8
-        best_order = None
-        for lanes, ks, clu in itertools.product((32, 16, 8), (1, 2, 4, 8), (False, True)):
-            if (ks > 1 and kv // ks < lanes) or (clu and not 1 < ks <= 8) or (quick and clu):
-                continue
-            tiles, total = {}, 0.0
-            for m in skinny_ms:
-                x, _ = timing.make_input(kind, m, k, dev)
-                out = torch.empty(m, n, device=dev, dtype=x.dtype)
-                bt = None
-                for tile in SKINNY_TILES:
-                    pl = Plan(skinny=SkinnyOrder(lanes_per_row=lanes, ksplit=ks, default_tile=tile, cluster=clu),
-                              skinny_max_m=L.SKINNY_MAX_TOKENS)
-                    pf = (lambda nxt: {"prefetch": nxt, "prefetch_bytes": prefetch_bytes}) if prefetch_bytes else (lambda nxt: {})
-                    t = timing.time_per_call(lambda w, kw, nxt: L.gemm(x, w, out=out, plan=pl, **pf(nxt)), cold, calls=calls, replays=replays)
-                    if bt is None or t < bt[0]:
-                        bt = (t, tile)
-                tiles[m] = bt
-                total += bt[0]
-            if best_order is None or total < best_order[0]:
-                best_order = (total, lanes, ks, clu, tiles)
-        if best_order is not None and skinny_ms:
-            _, lanes, ks, clu, tiles = best_order
-            plan.skinny = SkinnyOrder(lanes_per_row=lanes, ksplit=ks, cluster=clu, tiles={m: t for m, (_, t) in tiles.items()})
-            plan.skinny_max_m = 0
-            for m in skinny_ms:
-                if tiles[m][0] < tc_us[m]:
-                    plan.skinny_max_m = m
-                else:
+        winner = None
+        for choice in tc_space(kind, m, n, k, sm_count, quick):
+            t = bench.microseconds(m, Plan(tc={m: choice}))
+            if t is not None and (winner is None or t < winner[0]):
+                winner = (t, choice)
+        tc_time[m], plan.tc[m] = winner
+        log(f"  {kind} {n}x{k} M={m}: {winner[0]:.2f} us  {winner[1]}")
+    small = [m for m in tokens if m <= min(skinny_tokens, L.SKINNY_MAX_TOKENS)]
+    if kind in ("bf16", "f16") and small:
+        best = None  # (summed time, order fields, {m: (time, tile)})
+        for lanes, ks, cluster, tiles in skinny_space(k, quick):
+            per_m, total = {}, 0.0
+            for m in small:
+                timed = [(bench.microseconds(m, Plan(skinny=SkinnyOrder(lanes, ks, default_tile=t, cluster=cluster),
+                                                     skinny_max_m=L.SKINNY_MAX_TOKENS), with_scales=False), t) for t in tiles]
+                timed = [(us, t) for us, t in timed if us is not None]
+                if not timed:
                     break
-            log(f"  {kind} {n}x{k} skinny lanes={lanes} ksplit={ks} cluster={clu} max_m={plan.skinny_max_m} "
-                + " ".join(f"M{m}:{tiles[m][0]:.2f}" for m in skinny_ms))
-    del cold
-    torch.cuda.empty_cache()
+                per_m[m] = min(timed, key=lambda e: e[0])
+                total += per_m[m][0]
+            if len(per_m) == len(small) and (best is None or total < best[0]):
+                best = (total, (lanes, ks, cluster), per_m)
+        if best is not None:
+            _, (lanes, ks, cluster), per_m = best
+            plan.skinny = SkinnyOrder(lanes_per_row=lanes, ksplit=ks, cluster=cluster, tiles={m: t for m, (_, t) in per_m.items()},
+                                      default_tile=per_m[small[0]][1])
+            plan.skinny_max_m = 0
+            for m in small:  # skinny serves 1..m while it keeps beating the tensor cores
+                if per_m[m][0] >= tc_time[m]:
+                    break
+                plan.skinny_max_m = m
+            log(f"  {kind} {n}x{k} skinny lanes={lanes} ksplit={ks} cluster={cluster} max_m={plan.skinny_max_m} "
+                + " ".join(f"M{m}:{per_m[m][0]:.2f}" for m in small))
+    bench.close()
     return plan
+
+
+def _read_plans(path: str) -> dict:
+    if not os.path.isfile(path):
+        return {}
+    out = {}
+    for key, d in json.load(open(path)).get("plans", {}).items():
+        kind, shape = key.split(":")
+        n, k = (int(v) for v in shape.split("x"))
+        out[(kind, n, k)] = Plan.from_json(d)
+    return out
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--shapes", required=True, help='JSON {"shapes": [{"name", "n", "k"}, ...]}')
+    ap.add_argument("--shapes", required=True, help='JSON {"shapes": [{"name", "n", "k", optional "kinds", "max_m"}, ...]}')
     ap.add_argument("--kinds", default="bf16")
     ap.add_argument("--out", required=True)
     ap.add_argument("--tokens", default="1,2,4,8,16,32,64,128,256")
@@ -124,6 +185,7 @@ def main() -> None:
     ap.add_argument("--quick", action="store_true", help="smaller candidate grid")
     ap.add_argument("--pdl", action="store_true")
     ap.add_argument("--prefetch-next-mb", type=float, default=0, help="every call prefetches this much of the next weight into L2")
+    ap.add_argument("--skinny-tokens", type=int, default=2, help="largest token count the skinny engine is tried at")
     args = ap.parse_args()
 
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -131,26 +193,18 @@ def main() -> None:
     L.set_pdl(args.pdl)
     tokens = [int(t) for t in args.tokens.split(",")]
     shapes = json.load(open(args.shapes))["shapes"]
-    max_n = max(s["n"] for s in shapes)
-    L.reserve_workspace(dev, max(KSPLITS) * max(tokens) * max_n, 4 * max_n)
-    plans: dict[tuple[str, int, int], Plan] = {}
-    if os.path.isfile(args.out):  # resume
-        for key, d in json.load(open(args.out)).get("plans", {}).items():
-            kind, shape = key.split(":")
-            n, k = (int(v) for v in shape.split("x"))
-            plans[(kind, n, k)] = Plan.from_json(d)
+    widest = max(s["n"] for s in shapes)
+    L.reserve_workspace(dev, max(KSPLITS) * max(tokens) * widest, 4 * widest)
+    plans = _read_plans(args.out)  # resume
     for kind in args.kinds.split(","):
         for s in shapes:
             n, k = s["n"], s["k"]
-            if (kind, n, k) in plans or k % L.KINDS[kind][2]:
+            if (kind, n, k) in plans or k % L.KINDS[kind][2] or (s.get("kinds") and kind not in s["kinds"]):
                 continue
-            only = s.get("kinds")
-            if only and kind not in only:
-                continue
-            toks = [t for t in tokens if t <= s.get("max_m", 1 << 30)]
             print(f"{kind} {s.get('name', '')} {n}x{k}", flush=True)
-            plans[(kind, n, k)] = tune_shape(kind, n, k, toks, dev, args.replays, args.max_calls, args.quick,
-                                             prefetch_bytes=int(args.prefetch_next_mb * (1 << 20)))
+            plans[(kind, n, k)] = search(kind, n, k, [t for t in tokens if t <= s.get("max_m", 1 << 30)], dev, args.replays,
+                                         args.max_calls, args.quick, prefetch_bytes=int(args.prefetch_next_mb * (1 << 20)),
+                                         skinny_tokens=args.skinny_tokens)
             L.save_plans(args.out, plans, name)
 
 
