@@ -67,6 +67,12 @@ class DecodeLayer:
         self.kind, self.shape, self.tp, self.rank = kind, shape, tp, rank
         g = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
         self.w = {name: timing.make_weight(kind, n, k, g, device) for name, (n, k) in shape.shards(tp).items()}
+        if kind in ("bf16", "f16"):
+            # 16-bit weights of N(0, 0.02) grow the hidden state by 0.02 * sqrt(K) per projection and overflow within a
+            # few layers of the residual stream: rescale to 0.5 / sqrt(full K) so that values stay finite (timing is
+            # value-independent, the check against NCCL is not)
+            full_k = {"qkv": shape.hidden, "o": shape.hidden, "gate_up": shape.hidden, "down": shape.inter}
+            self.w = {name: (w * (0.5 / (0.02 * full_k[name] ** 0.5)), kw) for name, (w, kw) in self.w.items()}
 
     def weight_bytes(self) -> int:
         return sum(timing.weight_bytes(self.kind, *nk) for nk in self.shape.shards(self.tp).values())
