@@ -216,18 +216,26 @@ template <class G, int ATOMS, bool BF16>
 __device__ __forceinline__ void w8_widen_stage(uint32_t st, uint32_t abuf, int r, int part) {
   constexpr int kChunks = 8 / G::kSubParts;
 #pragma unroll
-  for (int a = 0; a < ATOMS; ++a)
+  for (int a = 0; a < ATOMS; ++a) {
+    // all of the atom's shared-memory reads first, so that their latencies overlap instead of each sitting in front
+    // of its own conversion (the loads and the tensor-memory stores are ordered instructions)
+    uint4 raw[kChunks];
 #pragma unroll
     for (int cc = 0; cc < kChunks; ++cc) {
       const int c = part * kChunks + cc;
-      const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+      raw[cc] = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+    }
+#pragma unroll
+    for (int cc = 0; cc < kChunks; ++cc) {
+      const int c = part * kChunks + cc;
       uint32_t o[8];
-      widen_e4m3x4<BF16>(raw.x, o[0], o[1]);
-      widen_e4m3x4<BF16>(raw.y, o[2], o[3]);
-      widen_e4m3x4<BF16>(raw.z, o[4], o[5]);
-      widen_e4m3x4<BF16>(raw.w, o[6], o[7]);
+      widen_e4m3x4<BF16>(raw[cc].x, o[0], o[1]);
+      widen_e4m3x4<BF16>(raw[cc].y, o[2], o[3]);
+      widen_e4m3x4<BF16>(raw[cc].z, o[4], o[5]);
+      widen_e4m3x4<BF16>(raw[cc].w, o[6], o[7]);
       tmem_st8(abuf + a * G::kAColsAtom + c * 8, o);
     }
+  }
 }
 
 // W4A16: one thread's share of a stage. Row r of every atom is 128 bytes = 8 chunks of 32 K elements; chunk c holds
@@ -239,22 +247,34 @@ __device__ __forceinline__ void w4_widen_stage(uint32_t st, uint32_t abuf, int r
   static_assert(kChunks % 2 == 0, "scales are fetched four at a time");
 #pragma unroll
   for (int a = 0; a < ATOMS; ++a) {
+    // the atom's shared-memory reads first (weights and scales), then the arithmetic: see w8_widen_stage
+    uint4 raw[kChunks];
+    uint32_t sc4[kChunks / 2];
 #pragma unroll
     for (int cp = 0; cp < kChunks / 2; ++cp) {
       const int c0 = part * kChunks + 2 * cp;
-      uint32_t sc4, sc[4];
-      asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc4) : "r"(st + G::kSfAOff + a * 2048 + r * 16 + 2 * c0));
-      widen_scales4<BF16>(sc4, sc);
+      asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc4[cp]) : "r"(st + G::kSfAOff + a * 2048 + r * 16 + 2 * c0));
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = c0 + cc;
-        const uint4 raw = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+        raw[2 * cp + cc] = lds128(st + G::kAOff + a * kAAtomTile + r * 128 + ((c ^ (r & 7)) << 4));
+      }
+    }
+#pragma unroll
+    for (int cp = 0; cp < kChunks / 2; ++cp) {
+      const int c0 = part * kChunks + 2 * cp;
+      uint32_t sc[4];
+      widen_scales4<BF16>(sc4[cp], sc);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = c0 + cc;
+        const uint4 rw = raw[2 * cp + cc];
         uint32_t o[8];
-        widen_e2m1x8<BF16>(raw.x, sc[cc * 2], o);
-        widen_e2m1x8<BF16>(raw.y, sc[cc * 2], o + 4);
+        widen_e2m1x8<BF16>(rw.x, sc[cc * 2], o);
+        widen_e2m1x8<BF16>(rw.y, sc[cc * 2], o + 4);
         tmem_st8(abuf + a * G::kAColsAtom + c * 16, o);
-        widen_e2m1x8<BF16>(raw.z, sc[cc * 2 + 1], o);
-        widen_e2m1x8<BF16>(raw.w, sc[cc * 2 + 1], o + 4);
+        widen_e2m1x8<BF16>(rw.z, sc[cc * 2 + 1], o);
+        widen_e2m1x8<BF16>(rw.w, sc[cc * 2 + 1], o + 4);
         tmem_st8(abuf + a * G::kAColsAtom + c * 16 + 8, o);
       }
     }
