@@ -57,7 +57,7 @@ enum { LLG_DT_NONE = 0, LLG_DT_BF16 = 1, LLG_DT_F16 = 2, LLG_DT_F32 = 3 };
 /* Quantizer modes; values equal the reference's enum QuantMode (csrc/quant.h:9-14). */
 enum { LLG_QUANT_FP8_STATIC = 0, LLG_QUANT_FP8_PER_TOKEN = 1, LLG_QUANT_INT8_PER_TOKEN = 2, LLG_QUANT_NVFP4 = 3 };
 
-#define LLG_NUM_CFGS 10
+#define LLG_NUM_CFGS 12
 #define LLG_MAX_STAGES 16
 #define LLG_SKINNY_MAX_TOKENS 16
 
@@ -96,7 +96,10 @@ LLG_API int32_t llg_skinny_ranges(int32_t N, int32_t ksplit);
  *   v = v + bias[p or q]                                               (rounded add, no fused multiply-add)
  * stored as y[q,p] when swap else y[p,q]. INT8 accumulates in int32 (exact) and converts once.
  * Stands in for torch.ops.lowlat_gemm.tc_gemm (reference csrc/ops.cpp:201-300, 393-401; descriptor
- * csrc/tc_params.h:28-60; kernel csrc/tc_gemm.cuh:179-501). */
+ * csrc/tc_params.h:28-60; kernel csrc/tc_gemm.cuh:179-501).
+ * Tile configs: 0-4 = 128 x {16,32,64,128,256} with one 128-byte K atom per pipeline stage, 5-9 = the same with two;
+ * 10, 11 = 256 x {128,256} computed by a pair of CTAs (the large tiles, reference csrc/tc_gemm.cuh:92-101): bf16, f16,
+ * fp8 and int8 only, ksplit must be 1. */
 typedef struct llg_tc_args {
   int32_t kind;                  /* LLG_KIND_* */
   int32_t cfg, stages, ksplit;   /* tile config [0, LLG_NUM_CFGS), pipeline depth (clamped), K partitions [1,64] */

@@ -173,8 +173,9 @@ unsigned int* status_word_device_ptr() {
 
 TcTile tc_tile_of(int cfg) {
   static const int bq[5] = {16, 32, 64, 128, 256};
-  if (cfg < 0 || cfg >= LLG_NUM_CFGS) return {0, 0};
-  return {bq[cfg % 5], 1 + cfg / 5};
+  if (cfg < 0 || cfg >= LLG_NUM_CFGS) return {0, 0, 0};
+  if (cfg >= 10) return {cfg == 10 ? 128 : 256, 1, 1};  // 256-row tiles on CTA pairs
+  return {bq[cfg % 5], 1 + cfg / 5, 0};
 }
 
 int tc_family_of(int kind) {
@@ -198,6 +199,8 @@ int tc_threads_of(int kind) {
 }
 
 int tc_stage_bytes_of(int kind, int cfg) {
+  const TcTile t = tc_tile_of(cfg);
+  if (t.pair) return tc_pair_stage_bytes(tc_family_of(kind), t.bq);
   switch (tc_family_of(kind)) {
     case FAM_F16: return tc_stage_bytes_f16(cfg);
     case FAM_F8: return tc_stage_bytes_f8(cfg);
@@ -264,9 +267,9 @@ int llg_device_status(uint32_t* status) {
 int llg_tc_info(int32_t kind, int32_t cfg, int32_t out[4]) {
   const TcTile t = tc_tile_of(cfg);
   if (t.bq == 0 || tc_family_of(kind) < 0) return fail(LLG_E_INVALID, "unknown kind %d or cfg %d", kind, cfg);
-  out[0] = 128;
+  out[0] = t.pair ? 256 : 128;
   out[1] = t.bq;
-  out[2] = tc_threads_of(kind);
+  out[2] = t.pair ? 192 : tc_threads_of(kind);
   out[3] = tc_stage_bytes_of(kind, cfg);
   return LLG_OK;
 }
@@ -406,6 +409,8 @@ static int tc_gemm_run(const llg_tc_args* a, const llg_push_args* push, void* st
   const bool cluster = a->cluster && a->ksplit > 1;
   if (cluster && a->ksplit > 8) return fail(LLG_E_INVALID, "cluster split-K supports ksplit <= 8, got %d", a->ksplit);
   const TcTile tile = tc_tile_of(a->cfg);
+  if (tile.pair && (a->ksplit > 1 || push))
+    return fail(LLG_E_CONFIG, "config %d (256-row tiles on CTA pairs) runs without split-K and without the pushing epilogue", a->cfg);
   if (a->ksplit > 1 && !cluster) {
     const int64_t tiles = ((P + 127) / 128) * ((Q + tile.bq - 1) / tile.bq);
     if (!a->ws || !a->counters) return fail(LLG_E_INVALID, "workspace must be a contiguous 4-byte tensor, counters contiguous int32");
@@ -444,21 +449,22 @@ static int tc_gemm_run(const llg_tc_args* a, const llg_push_args* push, void* st
     p.y = push->dst[push->rank];
   }
   const uint32_t bq = (uint32_t)tile.bq;
+  const uint32_t shape = ((bq >> 3) << 17) | (((tile.pair ? 256u : 128u) >> 4) << 24);  // N / 8 and M / 16 of one MMA
   switch (a->kind) {
     case LLG_KIND_BF16: case LLG_KIND_W8A16_BF16: case LLG_KIND_W4A16_BF16:
-      p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((bq >> 3) << 17) | ((128u >> 4) << 24); p.bf16_act = 1; break;
+      p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | shape; p.bf16_act = 1; break;
     case LLG_KIND_F16: case LLG_KIND_W8A16_F16: case LLG_KIND_W4A16_F16:
-      p.idesc = (1u << 4) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;
-    case LLG_KIND_FP8: p.idesc = (1u << 4) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;          // e4m3 = format 0
-    case LLG_KIND_INT8: p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;
-    case LLG_KIND_NVFP4: p.idesc = (1u << 7) | (1u << 10) | ((bq >> 3) << 17) | ((128u >> 4) << 24); break;  // e2m1, ue4m3 scales
+      p.idesc = (1u << 4) | shape; break;
+    case LLG_KIND_FP8: p.idesc = (1u << 4) | shape; break;          // e4m3 = format 0
+    case LLG_KIND_INT8: p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | shape; break;
+    case LLG_KIND_NVFP4: p.idesc = (1u << 7) | (1u << 10) | shape; break;  // e2m1, ue4m3 scales
   }
 
   // Row pitch of the A tiles. A 128-row MMA tile may own fewer rows: with a whole K range per CTA (no split-K) the
   // pitch is shrunk until the tiles fill the last round of SMs evenly, e.g. 14336 rows -> 148 tiles of 97 rows instead
   // of 112 tiles of 128 on 148 SMs. The TMA box is as tall as the pitch; the MMA still spans 128 rows.
   p.p_rows = 128;
-  if (a->ksplit == 1 && !cluster && a->swap) {
+  if (a->ksplit == 1 && !cluster && a->swap && !tile.pair) {
     const int64_t sms = sm_count() > 0 ? sm_count() : 1;
     const int64_t tq = (Q + tile.bq - 1) / tile.bq, tp0 = (P + 127) / 128;
     const int64_t rounds = (tp0 * tq + sms - 1) / sms;
@@ -470,8 +476,9 @@ static int tc_gemm_run(const llg_tc_args* a, const llg_push_args* push, void* st
     }
   }
   CUtensorMap ta, tb;
+  // boxes: a CTA's rows of A and its rows of B (a CTA of a pair holds half of the B tile)
   if (!make_map(&ta, a->a, a->a_row_bytes, P, a->lda_bytes, p.p_rows, p.a_is_weight) ||
-      !make_map(&tb, a->b, a->b_row_bytes, Q, a->ldb_bytes, tile.bq, !p.a_is_weight))
+      !make_map(&tb, a->b, a->b_row_bytes, Q, a->ldb_bytes, tile.pair ? tile.bq / 2 : tile.bq, !p.a_is_weight))
     return fail(LLG_E_CUDA, "cuTensorMapEncodeTiled failed (operand layout not expressible as a TMA map)");
 
   CUtensorMap ts = ta, tt = tb;  // only read when sf_tma is set
@@ -488,7 +495,8 @@ static int tc_gemm_run(const llg_tc_args* a, const llg_push_args* push, void* st
   const bool pdl = pdl_on();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  switch (tc_family_of(a->kind)) {
+  if (tile.pair) e = tc_launch_pair(fam, ta, tb, p, tile.bq, pdl, s);
+  else switch (fam) {
     case FAM_F16: e = tc_launch_f16(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
     case FAM_F8: e = tc_launch_f8(ta, tb, ts, tt, p, a->cfg, pdl, s); break;
     case FAM_I8: e = tc_launch_i8(ta, tb, ts, tt, p, a->cfg, pdl, s); break;

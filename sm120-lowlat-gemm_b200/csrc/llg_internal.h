@@ -163,8 +163,9 @@ struct TcDev {
 };
 
 struct TcTile {
-  int bq;      // 16, 32, 64, 128, 256 (BP is always 128)
+  int bq;      // 16, 32, 64, 128, 256
   int atoms;   // 128-byte K atoms of the A operand per pipeline stage (1 or 2)
+  int pair;    // 1: a 256 x bq tile computed by a pair of CTAs (tcgen05 cta_group::2); 0: 128 x bq on one CTA
 };
 TcTile tc_tile_of(int cfg);
 int tc_family_of(int kind);
@@ -172,6 +173,10 @@ int tc_family_of(int kind);
 int tc_stage_bytes_of(int kind, int cfg);
 int tc_threads_of(int kind);  // 192, or 320 for the kinds with helper warps (block scales / widening)
 constexpr int kSmemBudget = 227 * 1024 - 2048;  // dynamic shared memory for stages; the rest holds barriers and slack
+
+// 256-row tiles on CTA pairs (umma_pair.cu): families F16, F8 and I8, bq 128 or 256, no split-K.
+cudaError_t tc_launch_pair(int family, const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int bq, bool pdl, cudaStream_t s);
+int tc_pair_stage_bytes(int family, int bq);  // 0 when the family has no pair kernel
 
 // Defined per family in umma_<family>.cu.
 cudaError_t tc_launch_f16(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ts, const CUtensorMap& tt, const TcDev& p, int cfg, bool pdl, cudaStream_t s);

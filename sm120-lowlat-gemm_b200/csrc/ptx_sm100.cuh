@@ -112,6 +112,11 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
+__device__ __forceinline__ uint64_t policy_evict_normal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 __device__ __forceinline__ uint64_t policy_evict_last() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
@@ -322,6 +327,68 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
       : "=r"(r)
       : "f"(hi), "f"(lo));
   return r & 0xffu;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// CTA pairs (cta_group::2): the two CTAs of a cluster (1 x 2) run one 256-row MMA. Each holds its 128 rows of A, its
+// half of B and its 128 lanes of the accumulator; the CTA of cluster rank 0 issues the MMAs for both. Loads never use
+// multicast: each CTA fetches its own operands and reports the bytes to the issuing CTA's barrier.
+
+// One warp of EACH CTA of the pair executes the allocation (same warp index, same holder address) and the release.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t holder_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// 2-D tiled load into THIS CTA's shared memory whose bytes are counted on `bar`, a shared::cluster address that may
+// lie in the other CTA of the pair (mapa).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+
+// D[tmem of both CTAs] (+)= A * B with both operands in the shared memory of both CTAs (same offsets in each).
+#define LLG_MMA_SS_PAIR(KINDSTR)                                                                         \
+  asm volatile(                                                                                          \
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                  \
+      "tcgen05.mma.cta_group::2.kind::" KINDSTR " [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),           \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)                                               \
+      : "memory")
+__device__ __forceinline__ void mma_pair_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  LLG_MMA_SS_PAIR("f16");
+}
+__device__ __forceinline__ void mma_pair_f8f6f4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  LLG_MMA_SS_PAIR("f8f6f4");
+}
+__device__ __forceinline__ void mma_pair_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  LLG_MMA_SS_PAIR("i8");
+}
+#undef LLG_MMA_SS_PAIR
+
+// Arrives on the mbarrier at this shared-memory offset in every CTA of `cta_mask` once the pair's MMAs issued so far
+// have completed (a barrier signal fanned out to both CTAs; no data moves).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(cta_mask)
+               : "memory");
+}
+
+// Arrive on an mbarrier of any CTA of the cluster (address from cluster_map_shared).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 }  // namespace llg

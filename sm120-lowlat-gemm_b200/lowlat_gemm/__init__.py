@@ -18,7 +18,7 @@ include/llg_core.h); nothing falls back to the CPU or to a vendor GEMM.
 from .api import (_FP4_KINDS, _workspace, _ws, gemm, kind_of, pdl_enabled, quantize_fp8, quantize_int8,  # noqa: F401
                   quantize_nvfp4, reserve_workspace, set_pdl, silu_mul, silu_mul_quantize_fp8, silu_mul_quantize_nvfp4, supports,
                   workspace_need)
-from .plans import (KINDS, MAX_STAGES, NUM_CFGS, SKINNY_MAX_TOKENS, _MIXED, Plan, SkinnyOrder, SkinnyTile,  # noqa: F401
+from .plans import (KINDS, MAX_STAGES, NUM_CFGS, PAIR_CFGS, SKINNY_MAX_TOKENS, _MIXED, Plan, SkinnyOrder, SkinnyTile,  # noqa: F401
                     TcChoice, _file_key, _nearest, _packaged_path, _tc_lookup, cfg_atoms, default_plan,
                     default_skinny_order, default_tc_choice, get_plan, load_plans, max_stages, prefer_lowlat,
                     save_plans, set_plan, skinny_ranges, smem_budget, tc_info)

@@ -3,8 +3,9 @@
 Surface and semantics follow the reference's planner (lowlat_gemm/__init__.py:83-349): the dataclasses with their
 validation and JSON form, the "largest tuned M <= m, valid up to twice the largest tuned M" lookup, a per-device-name
 registry filled from set_plan(), LLG_PLAN_FILE, the packaged plans/<device>.json and finally heuristics. The tile
-table and the heuristics themselves are B200's: every config is a 128-row tcgen05 tile (128 x {16,32,64,128,256},
-one or two 128-byte K atoms per pipeline stage) and the shared-memory budget is the 227 KB of sm_100.
+table and the heuristics themselves are B200's: configs 0-9 are 128-row tcgen05 tiles (128 x {16,32,64,128,256}, one
+or two 128-byte K atoms per pipeline stage), configs 10 and 11 are 256 x {128,256} tiles computed by a pair of CTAs
+(bf16, f16, fp8, int8; no split-K), and the shared-memory budget is the 227 KB of sm_100.
 """
 
 from __future__ import annotations
@@ -21,7 +22,8 @@ import torch
 from . import _native as N
 
 SKINNY_MAX_TOKENS = 16
-NUM_CFGS = 10
+NUM_CFGS = 12
+PAIR_CFGS = (10, 11)  # 256-row tiles on CTA pairs
 MAX_STAGES = 16
 
 # kind -> (id, K elements per 128-byte atom of the streamed operand, K multiple required)
@@ -92,6 +94,8 @@ class TcChoice:
             raise ValueError(f"bad ksplit/stages {self.ksplit}/{self.stages}")
         if self.cluster and self.ksplit > 8:
             raise ValueError(f"cluster split-K needs ksplit <= 8, got {self.ksplit}")
+        if self.cfg in PAIR_CFGS and self.ksplit > 1:
+            raise ValueError(f"cfg {self.cfg} (256-row tiles on CTA pairs) runs without split-K, got ksplit {self.ksplit}")
 
 
 @dataclass
@@ -178,7 +182,7 @@ def max_stages(kind: str, cfg: int) -> int:
 
 
 def cfg_atoms(cfg: int) -> int:
-    return 1 + cfg // 5
+    return 1 if cfg in PAIR_CFGS else 1 + cfg // 5
 
 
 def skinny_ranges(n: int, ksplit: int, sm_count: int) -> int:
@@ -203,6 +207,8 @@ def default_skinny_order(n: int, k: int, sm_count: int) -> SkinnyOrder:
 
 
 def _fit_cfg(kind: str, cfg: int) -> int:
+    if cfg in PAIR_CFGS and max_stages(kind, cfg) < 2:
+        cfg = 4 if cfg == 11 else 3  # the kind has no pair kernel: the single-CTA tile of the same width
     while max_stages(kind, cfg) < 2:
         cfg = cfg - 5 if cfg >= 5 else cfg - 1
         if cfg < 0:

@@ -193,12 +193,38 @@ def test_every_config_orientation_and_split(kind):
         x, w, kw, xd, wd = operands(kind, m, n, k, seed=m)
         ref = xd @ wd.T
         for cfg, swap, ksplit in itertools.product(range(L.NUM_CFGS), (False, True), (1, 3)):
-            if L.max_stages(kind, cfg) < 2 or (kind in L._MIXED and not swap):
+            if L.max_stages(kind, cfg) < 2 or (kind in L._MIXED and not swap) or (cfg in L.PAIR_CFGS and ksplit > 1):
                 continue
             c = TcChoice(cfg=cfg, swap=swap, stages=min(3, L.max_stages(kind, cfg)), ksplit=ksplit)
             y = L.gemm(x, w, out_dtype=torch.float32, plan=Plan(tc={m: c}), **kw)
             e = rel_err(y, ref)
             assert e < TOL, f"{kind} m={m} {c}: rel err {e}"
+    no_expired_wait()
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f16", "fp8", "int8"])
+def test_tiles_on_cta_pairs(kind):
+    """The 256-row tiles that a pair of CTAs computes together: both orientations, ragged edges on every side (rows that
+    leave the second CTA of a pair without data, columns that leave it without its half of B, a K tail), rings of 2 and
+    5 stages, 16-bit outputs (vector stores) equal to the rounded fp32 result, bias on either side; INT8 bit-identical to
+    the single-CTA tile. The last shape gives every pair several tiles, so both accumulator buffers are reused."""
+    out16 = torch.float16 if kind == "f16" else torch.bfloat16
+    for m, n, k in [(300, 712, 2 * 256 + KIND_K[kind]), (129, 130, 256), (520, 1100, 3 * 256), (2048, 2560, 512)]:
+        x, w, kw, xd, wd = operands(kind, m, n, k, seed=m)
+        bias = torch.randn(n, generator=torch.Generator().manual_seed(m)).to(DEV)
+        ref = xd @ wd.T + bias.double().cpu().numpy()
+        # the epilogue multiplies by the scale of the MMA's row side first, so bits are compared within an orientation
+        single = {sw: L.gemm(x, w, bias=bias, out_dtype=torch.float32, plan=Plan(tc={m: TcChoice(cfg=3, swap=sw, stages=3)}), **kw)
+                  for sw in (False, True)}
+        for cfg, swap, stages in itertools.product(L.PAIR_CFGS, (False, True), (2, 5)):
+            plan = Plan(tc={m: TcChoice(cfg=cfg, swap=swap, stages=stages)})
+            y = L.gemm(x, w, bias=bias, out_dtype=torch.float32, plan=plan, **kw)
+            e = rel_err(y, ref)
+            assert e < TOL, f"{kind} {m}x{n}x{k} cfg={cfg} swap={swap} stages={stages}: rel err {e}"
+            if kind == "int8":
+                assert torch.equal(y, single[swap])
+            y16 = L.gemm(x, w, bias=bias, out_dtype=out16, plan=plan, **kw)
+            assert torch.equal(y16, y.to(out16)), f"{kind} cfg={cfg} swap={swap}: 16-bit output is not the rounded fp32 result"
     no_expired_wait()
 
 
@@ -208,6 +234,8 @@ def test_deep_pipelines(kind):
     x, w, kw, xd, wd = operands(kind, m, n, k, seed=3)
     ref = xd @ wd.T
     for cfg, ksplit in itertools.product(range(L.NUM_CFGS), (1, 2)):
+        if cfg in L.PAIR_CFGS and ksplit > 1:
+            continue
         top = L.max_stages(kind, cfg)
         for stages in sorted({s for s in (2, 8, 12, top) if 2 <= s <= top}):
             c = TcChoice(cfg=cfg, swap=True, stages=stages, ksplit=ksplit)
@@ -297,7 +325,7 @@ def test_cluster_split_k_matches_workspace_bitwise(kind):
         ref = xd @ wd.T
         for cfg, swap, ksplit in itertools.product(range(L.NUM_CFGS), (False, True), (2, 5, 8)):
             st = L.max_stages(kind, cfg)
-            if st < 2 or (kind in L._MIXED and not swap) or -(-k // (L.KINDS[kind][1] * L.cfg_atoms(cfg))) < 1:
+            if st < 2 or (kind in L._MIXED and not swap) or cfg in L.PAIR_CFGS:
                 continue
             c = TcChoice(cfg=cfg, swap=swap, stages=min(3, st), ksplit=ksplit)
             y_ws = L.gemm(x, w, out_dtype=torch.float32, plan=Plan(tc={m: c}), **kw)

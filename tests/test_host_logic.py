@@ -32,13 +32,19 @@ def test_struct_layout_matches_library():
 
 
 def test_tc_info_table():
-    assert L.NUM_CFGS == 10
+    assert L.NUM_CFGS == 12 and L.PAIR_CFGS == (10, 11)
     for kind in L.KINDS:
-        for cfg in range(L.NUM_CFGS):
+        for cfg in range(10):
             bp, bq, threads, stage = L.tc_info(kind, cfg)
             want = 704 if kind.startswith("w4a16") else 448 if kind.startswith("w8a16") else 320 if kind == "nvfp4" else 192
             assert bp == 128 and bq == 16 << (cfg % 5) and threads == want
             assert stage % 1024 == 0 and (stage == 0) == (L.max_stages(kind, cfg) == 0)
+        for cfg, width in zip(L.PAIR_CFGS, (128, 256)):  # 256-row tiles on CTA pairs: unconverted operands only
+            bp, bq, threads, stage = L.tc_info(kind, cfg)
+            assert (bp, bq, threads) == (256, width, 192) and L.cfg_atoms(cfg) == 1
+            assert stage == ((128 + width // 2) * 128 if kind in ("bf16", "f16", "fp8", "int8") else 0)
+    with pytest.raises(ValueError, match="runs without split-K"):
+        L.TcChoice(cfg=10, swap=False, ksplit=2)
     assert L.tc_info("bf16", 0)[3] == 128 * 128 + 16 * 128
     assert L.tc_info("nvfp4", 4)[3] == 0 and L.tc_info("w4a16_bf16", 5)[3] == 0
     with pytest.raises(RuntimeError, match="lowlat_gemm: unknown kind"):
@@ -47,9 +53,9 @@ def test_tc_info_table():
 
 def test_validation_errors_come_from_the_library_with_prefix():
     a = N.TcArgs()
-    a.kind, a.cfg, a.ksplit = 0, 11, 1
+    a.kind, a.cfg, a.ksplit = 0, 12, 1
     assert N.lib.llg_tc_gemm(C.byref(a), None) == -1
-    assert N.lib.llg_last_error().decode().startswith("lowlat_gemm: cfg must be in [0, 10)")
+    assert N.lib.llg_last_error().decode().startswith("lowlat_gemm: cfg must be in [0, 12)")
     a.cfg, a.ksplit = 0, 65
     assert N.lib.llg_tc_gemm(C.byref(a), None) == -1 and b"ksplit must be in [1, 64]" in N.lib.llg_last_error()
     a.ksplit, a.a, a.lda_bytes = 1, 4096, 24
@@ -88,7 +94,7 @@ def test_dataclass_validation():
     for bad in [dict(lanes_per_row=4), dict(ksplit=65), dict(ksplit=16, cluster=True)]:
         with pytest.raises(ValueError):
             SkinnyOrder(**bad)
-    for bad in [dict(cfg=10, swap=True), dict(cfg=0, swap=True, stages=1), dict(cfg=0, swap=True, stages=17),
+    for bad in [dict(cfg=12, swap=True), dict(cfg=11, swap=True, ksplit=2), dict(cfg=0, swap=True, stages=1), dict(cfg=0, swap=True, stages=17),
                 dict(cfg=0, swap=True, ksplit=0), dict(cfg=0, swap=True, ksplit=9, cluster=True)]:
         with pytest.raises(ValueError):
             TcChoice(**bad)
