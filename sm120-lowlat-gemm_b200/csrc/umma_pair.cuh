@@ -33,6 +33,11 @@ struct PairGeo {
   static constexpr uint32_t kTxBytes = 2u * kStageBytes;  // both CTAs report to one barrier
   static constexpr int kAccBufs = 2;
   static constexpr int kTmemCols = kAccBufs * BQ;
+  // epilogue scratch behind the ring: per epilogue warp a 32 rows x 128 bytes transposition buffer, then the tile's
+  // column-side factors (scale and bias as fp32) for two tiles in flight
+  static constexpr int kOutBuf = 4 * 32 * 128;
+  static constexpr int kColVec = 2 * 2 * BQ * 4;
+  static constexpr int kEpiBytes = kOutBuf + kColVec;
 };
 
 struct PairHeader {
@@ -45,47 +50,19 @@ struct PairHeader {
 };
 static_assert(sizeof(PairHeader) <= kHeaderBytes, "header too large");
 
-// Scales, converts and stores 16 consecutive columns of one output row (the arithmetic of tc_finish_row).
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// v = ((acc * alpha) * row_scale[p]) * col_scale[q] (+ bias), each operation rounded: the arithmetic of tc_finish_row
+// with the column-side factors taken from the tile's vectors in shared memory.
 template <bool INT_ACC>
-__device__ __forceinline__ void pair_emit(const TcDev& prm, float alpha, float rs, float bias_p, int p, int q_first,
-                                          int nvalid, const uint32_t (&v)[16]) {
-  float o[16];
-#pragma unroll
-  for (int c = 0; c < 16; ++c) {
-    const int q = q_first + c < prm.Q ? q_first + c : prm.Q - 1;
-    o[c] = tc_finish_row<INT_ACC>(prm, alpha, rs, bias_p, q, v[c]);
-  }
-  if (!prm.swap && nvalid == 16) {
-    if (prm.out_dtype == LLG_DT_F32) {
-      float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q_first;
-      if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-        for (int c = 0; c < 16; c += 4) *reinterpret_cast<float4*>(dst + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-        return;
-      }
-    } else {
-      uint16_t* dst = static_cast<uint16_t*>(prm.y) + (int64_t)p * prm.ldy + q_first;
-      if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-        uint32_t w2[8];
-#pragma unroll
-        for (int c = 0; c < 16; c += 2) {
-          if (prm.out_dtype == LLG_DT_BF16) {
-            const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(o[c]), __float2bfloat16_rn(o[c + 1]));
-            w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
-          } else {
-            const __half2 t = __halves2half2(__float2half_rn(o[c]), __float2half_rn(o[c + 1]));
-            w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
-          }
-        }
-        *reinterpret_cast<uint4*>(dst) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
-        *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w2[4], w2[5], w2[6], w2[7]);
-        return;
-      }
-    }
-  }
-#pragma unroll
-  for (int c = 0; c < 16; ++c)
-    if (c < nvalid) tc_store(prm, p, q_first + c, o[c]);
+__device__ __forceinline__ float pair_finish(float alpha, float rs, float bias_p, bool has_bias, bool bias_on_p, float cs,
+                                             float cb, uint32_t bits) {
+  const float acc = INT_ACC ? (float)(int32_t)bits : __uint_as_float(bits);
+  float v = __fmul_rn(__fmul_rn(__fmul_rn(acc, alpha), rs), cs);
+  if (has_bias) v = __fadd_rn(v, bias_on_p ? bias_p : cb);
+  return v;
 }
 
 template <int FAM, int BQ>
@@ -206,36 +183,124 @@ umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncwarp();
   } else {
     // ================================ epilogue (both CTAs, 128 rows each) ================================
+    // A thread owns one accumulator row (a tensor-memory lane). Storing its 16-column pieces straight to y would make
+    // every store instruction touch 32 output rows; instead each warp turns 128 output bytes per row of its 32 rows
+    // around in shared memory and writes them out as whole 128-byte lines, four rows per instruction. The transposed
+    // (swap) orientation and outputs whose rows are not 16-byte aligned keep element stores.
     const int quarter = warp & 3;  // tensor-memory lanes this warp may read: [32 * quarter, +32)
     const int r = quarter * 32 + lane;
+    const int et = tid - 64;       // 0..127 over the epilogue threads
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t acc_empty_r0 = cluster_map_shared(smem_u32(&hdr->acc_empty[0]), 0);
+    const uint32_t obuf = stage0 + (uint32_t)S * G::kStageBytes + (uint32_t)quarter * 4096u;
+    float* const colvec = reinterpret_cast<float*>(smem_raw + (stage0 - raw_base) + (size_t)S * G::kStageBytes + G::kOutBuf);
     pdl_wait();
     const float alpha = prm.alpha_ptr ? prm.alpha * __ldg(prm.alpha_ptr) : prm.alpha;
+    const bool has_bias = prm.bias_dtype != LLG_DT_NONE, bias_on_p = prm.bias_on_p != 0;
+    const int esz = prm.out_dtype == LLG_DT_F32 ? 4 : 2;
+    const bool lines = !prm.swap && prm.push_n == 0 && (((uintptr_t)prm.y | (uintptr_t)(prm.ldy * esz)) & 15) == 0;
     uint32_t n_acc = 0;
     bool ok = true;
     for (int t = pair; t < ntile; t += npairs) {
       const uint32_t ab = n_acc & 1u;
-      const int p = (t % tiles_p) * 256 + (int)rank * 128 + r, q0 = (t / tiles_p) * BQ;
+      const int prow0 = (t % tiles_p) * 256 + (int)rank * 128, q0 = (t / tiles_p) * BQ;
+      const int p = prow0 + r;
       const int nq = min(BQ, prm.Q - q0);
       const bool row_ok = p < prm.P;
-      float rs = 1.f, bias_p = 0.f;
-      if (row_ok) {  // fetched while the MMAs still run
-        rs = tc_vec(prm.row_scale, prm.row_scale_len, p);
-        if (prm.bias_dtype != LLG_DT_NONE && prm.bias_on_p) bias_p = tc_bias(prm, p);
+      // column-side factors of the tile, fetched once per CTA while the MMAs still run
+      float* const cs = colvec + ab * 2 * BQ;
+      float* const cb = cs + BQ;
+      for (int c = et; c < BQ; c += 128) {
+        const int q = q0 + c < prm.Q ? q0 + c : prm.Q - 1;
+        cs[c] = tc_vec(prm.col_scale, prm.col_scale_len, q);
+        cb[c] = has_bias && !bias_on_p ? tc_bias(prm, q) : 0.f;
       }
+      float rs = 1.f, bias_p = 0.f;
+      if (row_ok) {
+        rs = tc_vec(prm.row_scale, prm.row_scale_len, p);
+        if (has_bias && bias_on_p) bias_p = tc_bias(prm, p);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the vectors are complete (the other buffer belongs to the previous tile)
       if (ok) {
         ok = mbar_wait(smem_u32(&hdr->acc_full[ab]), (n_acc >> 1) & 1u, abort_word);
         if (!ok) give_up(prm, ST_EPILOGUE_WAIT);
       }
       tc_fence_after();
-      if (ok) {
+      if (ok && lines) {
+        const int blk = 128 / esz;  // columns per 128 output bytes: 64 (16-bit) or 32 (fp32)
+        for (int b0 = 0; b0 < nq; b0 += blk) {
+          uint32_t v[4][16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (j * 16 < blk && b0 + j * 16 < nq) tmem_ld16(tmem + lane_addr + ab * BQ + b0 + j * 16, v[j]);
+          tmem_wait_ld();
+          __syncwarp();  // the warp has read the previous block out of its buffer
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (j * 16 < blk && b0 + j * 16 < nq) {
+              float o[16];
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                o[c] = pair_finish<kIntAcc>(alpha, rs, bias_p, has_bias, bias_on_p, cs[b0 + j * 16 + c], cb[b0 + j * 16 + c], v[j][c]);
+              // 16-byte pieces of the row, XOR-swizzled by the row so that neither the writes (one row per lane) nor the
+              // reads (eight lanes per row) collide on banks
+              if (esz == 4) {
+#pragma unroll
+                for (int h = 0; h < 4; ++h)
+                  sts128(obuf + lane * 128 + (((j * 4 + h) ^ (lane & 7)) << 4),
+                         make_uint4(__float_as_uint(o[4 * h]), __float_as_uint(o[4 * h + 1]), __float_as_uint(o[4 * h + 2]),
+                                    __float_as_uint(o[4 * h + 3])));
+              } else {
+                uint32_t w2[8];
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                  if (prm.out_dtype == LLG_DT_BF16) {
+                    const __nv_bfloat162 h2 = __halves2bfloat162(__float2bfloat16_rn(o[c]), __float2bfloat16_rn(o[c + 1]));
+                    w2[c / 2] = *reinterpret_cast<const uint32_t*>(&h2);
+                  } else {
+                    const __half2 h2 = __halves2half2(__float2half_rn(o[c]), __float2half_rn(o[c + 1]));
+                    w2[c / 2] = *reinterpret_cast<const uint32_t*>(&h2);
+                  }
+                }
+                sts128(obuf + lane * 128 + (((j * 2) ^ (lane & 7)) << 4), make_uint4(w2[0], w2[1], w2[2], w2[3]));
+                sts128(obuf + lane * 128 + (((j * 2 + 1) ^ (lane & 7)) << 4), make_uint4(w2[4], w2[5], w2[6], w2[7]));
+              }
+            }
+          }
+          __syncwarp();
+          const int piece = lane & 7, per = 16 / esz;  // this lane's 16-byte piece of a row; elements in it
+          const int col = b0 + piece * per;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = i * 4 + (lane >> 3), pr = prow0 + quarter * 32 + rl;
+            if (pr < prm.P && col < nq) {
+              const uint4 d = lds128(obuf + rl * 128 + ((piece ^ (rl & 7)) << 4));
+              unsigned char* const dst = static_cast<unsigned char*>(prm.y) + ((int64_t)pr * prm.ldy + q0 + col) * esz;
+              if (col + per <= nq) {
+                *reinterpret_cast<uint4*>(dst) = d;
+              } else {  // the ragged right edge: element by element
+                const uint32_t w4[4] = {d.x, d.y, d.z, d.w};
+                for (int e = 0; col + e < nq; ++e) {
+                  if (esz == 4) reinterpret_cast<uint32_t*>(dst)[e] = w4[e];
+                  else reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(w4[e >> 1] >> ((e & 1) * 16));
+                }
+              }
+            }
+          }
+        }
+      } else if (ok) {
         for (int c0 = 0; c0 < BQ; c0 += 16) {
           if (c0 >= nq) break;
           uint32_t v[16];
           tmem_ld16(tmem + lane_addr + ab * BQ + c0, v);
           tmem_wait_ld();
-          if (row_ok) pair_emit<kIntAcc>(prm, alpha, rs, bias_p, p, q0 + c0, min(16, nq - c0), v);
+          if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              if (c0 + c < nq)
+                tc_store(prm, p, q0 + c0 + c,
+                         pair_finish<kIntAcc>(alpha, rs, bias_p, has_bias, bias_on_p, cs[c0 + c], cb[c0 + c], v[c]));
+          }
         }
       }
       // the buffer may be overwritten by the MMAs of a later tile from here on
@@ -263,11 +328,12 @@ template <int FAM, int BQ>
 cudaError_t pair_launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& prm, bool pdl, cudaStream_t stream) {
   using G = PairGeo<BQ>;
   TcDev p = prm;
-  const int cap = kSmemBudget / G::kStageBytes < LLG_MAX_STAGES ? kSmemBudget / G::kStageBytes : LLG_MAX_STAGES;
+  constexpr int kRing = (kSmemBudget - G::kEpiBytes) / G::kStageBytes;
+  const int cap = kRing < LLG_MAX_STAGES ? kRing : LLG_MAX_STAGES;
   p.stages = prm.stages < 2 ? 2 : (prm.stages > cap ? cap : prm.stages);
   // at least half of an SM's shared memory, so that an SM never holds two CTAs of one launch (the second would sit in
   // its tensor-memory allocation until the first has walked all its tiles)
-  size_t smem = 1024 + kHeaderBytes + (size_t)p.stages * G::kStageBytes;
+  size_t smem = 1024 + kHeaderBytes + (size_t)p.stages * G::kStageBytes + G::kEpiBytes;
   if (smem < 116 * 1024) smem = 116 * 1024;
   static std::atomic<uint64_t> attr_done{0};  // one bit per device
   int dev = 0;
