@@ -177,8 +177,10 @@ def smem_budget() -> int:
 
 
 def max_stages(kind: str, cfg: int) -> int:
-    stage = tc_info(kind, cfg)[3]
-    return min(MAX_STAGES, smem_budget() // stage) if stage else 0
+    _, bq, _, stage = tc_info(kind, cfg)
+    # the pair kernel keeps its epilogue scratch (16 KB of line buffers and 16 bytes per tile column) behind the ring
+    budget = smem_budget() - (16384 + 16 * bq if cfg in PAIR_CFGS else 0)
+    return min(MAX_STAGES, budget // stage) if stage else 0
 
 
 def cfg_atoms(cfg: int) -> int:
@@ -230,10 +232,15 @@ def default_tc_choice(kind: str, m: int, n: int, k: int, sm_count: int) -> TcCho
     swap = kind in _MIXED or m <= 64
     if swap:
         cfg = 5 if m <= 16 else 6 if m <= 32 else 7 if m <= 64 else 3 if m <= 128 else 4
+    elif m >= 192 and n >= 256:
+        cfg = 11  # 256 x 256 on CTA pairs (measured on B200: fp8 14336x4096 at M = 256 / 1024 / 4096 25.5 / 60 / 175 us
+        #           against 27.8 / 75.8 / 266 us for the best single-CTA tile); kinds without a pair kernel fall back
     else:
         cfg = 4 if n >= 2048 and m >= 256 else 3
     cfg = _fit_cfg(kind, cfg)
     bp, bq, _, stage = tc_info(kind, cfg)
+    if cfg in PAIR_CFGS:
+        return TcChoice(cfg=cfg, swap=False, stages=max_stages(kind, cfg), ksplit=1)
     p, q = (n, m) if swap else (m, n)
     tiles = -(-p // bp) * -(-q // bq)
     nk = -(-k // (KINDS[kind][1] * cfg_atoms(cfg)))

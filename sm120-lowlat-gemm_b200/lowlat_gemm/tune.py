@@ -11,7 +11,8 @@ an interrupted run resumes from its --out.
 
 How it is organised here: a `Workbench` owns the cold weights of one (kind, N, K) and times one plan at one token
 count; `tc_space()` and `skinny_space()` enumerate the B200 search spaces (128-row tcgen05 tiles with one or two K
-atoms per stage, rings up to 227 KB, cluster or workspace split-K; persistent skinny CTAs of 8 or 16 warps);
+atoms per stage and 256-row tiles on CTA pairs, rings up to 227 KB, cluster or workspace split-K; persistent skinny
+CTAs of 8 or 16 warps);
 `search()` walks them. On B200 the skinny engine only competes at one or two tokens, so its space is searched up to
 --skinny-tokens (default 2).
 """
@@ -96,7 +97,7 @@ def tc_space(kind: str, m: int, n: int, k: int, sm_count: int, quick: bool = Fal
             if not quick:
                 depths |= {min(3, deepest), min(8, deepest)}
             for stages in sorted(depths):
-                for ks in KSPLITS:
+                for ks in ((1,) if cfg in L.PAIR_CFGS else KSPLITS):  # 256-row pair tiles have no split-K
                     if ks > 1 and (k_tiles // ks < 2 or tiles * ks > 6 * sm_count):
                         continue
                     if ks == 1 and tiles * 8 < sm_count and k_tiles >= 8:

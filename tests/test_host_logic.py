@@ -131,7 +131,7 @@ def test_heuristics_fill_the_gpu():
         assert stage > 0 and 2 <= c.stages <= L.max_stages(kind, c.cfg)
         assert c.swap == (kind in L._MIXED or m <= 64)
         p, q = (n, m) if c.swap else (m, n)
-        ctas = -(-p // bp) * -(-q // bq) * c.ksplit
+        ctas = -(-p // bp) * -(-q // bq) * c.ksplit * (2 if c.cfg in L.PAIR_CFGS else 1)  # a pair tile occupies two SMs
         assert ctas >= sms // 2 or kind == "int8"
     # what the tuner finds on B200 for the baseline shapes: two K atoms per stage for decode batches; the streaming
     # kinds unsplit with three stages where the row pitch can spread the tiles; small weights split over a cluster
