@@ -566,8 +566,11 @@ def run_tp(args) -> None:
         rel = float(((y_lib - y_ref).abs().max() / y_ref.abs().max().clamp_min(1e-6)).item())
         finite = bool(torch.isfinite(y_lib).all().item())
         rel = all_max(rel if finite else float("inf"))
-        # bf16 partials are rounded before NCCL adds them and the library adds them in fp32: a few bf16 ulps per layer
-        check.update(max_rel_diff=rel, ok=bool(rel < 3e-2))
+        # bf16 partials are rounded before NCCL adds them and the library adds them in fp32: a few bf16 ulps per layer.
+        # With NVFP4 activations such an ulp can move a value across a 4-bit quantization boundary in the next
+        # projection, so two equally valid orders of summation differ by a 4-bit step here and there: wider bound.
+        bound = 1e-1 if kind == "nvfp4" else 3e-2
+        check.update(max_rel_diff=rel, bound=bound, ok=bool(rel < bound))
         del ref_step
     run.capture()
     _progress("step captured")
