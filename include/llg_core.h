@@ -167,6 +167,15 @@ LLG_API int llg_gated_quant(const llg_gated_quant_args* args, void* stream);
 LLG_API void llg_set_pdl(int32_t on);
 LLG_API int32_t llg_pdl_enabled(void);
 
+/* Load-time conversion of a block-scale matrix (one e4m3 byte per 16 K elements) between the row-major form the
+ * entry points above take - [rows, cols] bytes, row pitch ld - and the tiled form of checkpoints prepared for
+ * block-scaled tensor-core GEMMs: tiles of 128 rows x 4 columns, 512 contiguous bytes each, byte (r, c) of a tile at
+ * (r % 32) * 16 + (r / 32) * 4 + c, row-tile major, rows and columns padded to whole tiles (padding written as zero).
+ * to_tiled = 0 reads the tiled buffer `src` and writes row-major `dst`; 1 the other way. The tiled buffer holds
+ * ceil(rows / 128) * ceil(cols / 4) * 512 bytes and must be 16-byte aligned. The reference takes row-major scales only
+ * (lowlat_gemm/__init__.py:10-16) and has no converter. */
+LLG_API int llg_sf_relayout(const void* src, void* dst, int32_t rows, int32_t cols, int64_t ld, int32_t to_tiled, void* stream);
+
 /* Host-buffer convenience used for end-to-end timing: copies x (HOST, pinned or pageable) to x_dev, runs the GEMM
  * described by `args` (whose activation operand must already point at x_dev), copies y back to y_host, all on
  * `stream`, without synchronising. No counterpart in the reference (its callers hold device tensors). */

@@ -6,8 +6,9 @@ bench.py's CPU-baseline legs may use it, and only as the checker or as the timed
 Pinning: the format decoders and the dequantised GEMM are checked against golden vectors produced by the reference's
 own CPU emulator of its tensor-core kernel (tests/emulate_tc.py) and the quantizers against the reference's test
 expressions (tests/test_gemm.py:200-218); see tests/golden/make_golden.py. The NVFP4 activation quantizer has no
-bit-level pin in the reference (its test only bounds the round-trip error, tests/test_gemm.py:221-228): for that one
-function parity is "unpinned" and rests on this restatement of csrc/quant.cu:85-114 alone.
+bit-level pin in the reference's CPU tests (its test only bounds the round-trip error, tests/test_gemm.py:221-228); it
+and the skinny summation order are pinned on the GPU instead, byte for byte against the reference's own kernels
+(csrc/quant.cu, csrc/gemv_lpr*.cu) compiled for sm_100a by oracle/Makefile (tests/test_gpu_ref_pin.py).
 
 Each function cites the reference lines it follows (paths relative to the reference repository).
 """
@@ -235,6 +236,32 @@ def splitk_sum_order(parts: np.ndarray) -> np.ndarray:
     for kk in range(1, parts.shape[0]):
         total = (total + parts[kk]).astype(parts.dtype)
     return total
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# block-scale layouts. The reference takes block scales row-major, [rows, K/16] (lowlat_gemm/__init__.py:10-16);
+# checkpoints prepared for block-scaled tensor-core GEMMs hold them in tiles of 128 rows x 4 columns (the published
+# layout of the vendor GEMM libraries' scale-factor operand): 512 contiguous bytes per tile, byte (r, c) of a tile at
+# (r % 32) * 16 + (r // 32) * 4 + c, tiles row-tile major, rows and columns padded to whole tiles with zeros.
+
+
+def sf_to_tiled(sf: np.ndarray) -> np.ndarray:
+    rows, cols = sf.shape
+    rt, ct = -(-rows // 128), -(-cols // 4)
+    out = np.zeros(rt * ct * 512, dtype=np.uint8)
+    for r in range(rows):
+        for c in range(cols):
+            out[((r // 128) * ct + c // 4) * 512 + ((r % 128) % 32) * 16 + ((r % 128) // 32) * 4 + c % 4] = sf[r, c]
+    return out
+
+
+def sf_from_tiled(tiled: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    ct = -(-cols // 4)
+    out = np.zeros((rows, cols), dtype=np.uint8)
+    for r in range(rows):
+        for c in range(cols):
+            out[r, c] = tiled[((r // 128) * ct + c // 4) * 512 + ((r % 128) % 32) * 16 + ((r % 128) // 32) * 4 + c % 4]
+    return out
 
 
 # ---------------------------------------------------------------------------------------------------------------

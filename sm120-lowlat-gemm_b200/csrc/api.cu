@@ -644,6 +644,20 @@ int llg_tc_gemm_static_ws(const llg_tc_args* args, void* stream) {
   return tc_gemm_run(&a, nullptr, stream);
 }
 
+int llg_sf_relayout(const void* src, void* dst, int32_t rows, int32_t cols, int64_t ld, int32_t to_tiled, void* stream) {
+  if (rows < 0 || cols < 0) return fail(LLG_E_INVALID, "scale relayout: negative size");
+  if (rows == 0 || cols == 0) return LLG_OK;
+  if (!src || !dst) return fail(LLG_E_INVALID, "scale relayout: null pointer");
+  if (ld < cols) return fail(LLG_E_INVALID, "scale relayout: row pitch %lld is shorter than a row of %d bytes", (long long)ld, cols);
+  if (!aligned(to_tiled ? dst : src, 16)) return fail(LLG_E_INVALID, "scale relayout: the tiled buffer needs 16-byte alignment");
+  const cudaError_t e = sf_relayout_launch(src, dst, rows, cols, ld, to_tiled != 0, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LLG_E_CUDA, "scale relayout launch failed: %s", cudaGetErrorString(e));
+  }
+  return LLG_OK;
+}
+
 int llg_tc_gemm_host(const llg_tc_args* args, const void* x_host, void* x_dev, int64_t x_bytes, void* y_host,
                      int64_t y_bytes, void* stream) {
   if (!args || !x_host || !x_dev || !y_host) return fail(LLG_E_INVALID, "null arguments");

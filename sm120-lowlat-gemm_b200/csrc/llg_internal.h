@@ -116,6 +116,10 @@ struct GatedExtra {
 };
 cudaError_t quant_launch(const llg_quant_args& a, const GatedExtra& g, cudaStream_t s);
 
+// ---- block-scale layouts (relayout.cu) ---------------------------------------------------------------------------
+// Row-major [rows, cols] bytes (row pitch ld) <-> tiles of 128 rows x 4 columns, 512 bytes each, padded to whole tiles.
+cudaError_t sf_relayout_launch(const void* src, void* dst, int rows, int cols, int64_t ld, bool to_tiled, cudaStream_t s);
+
 // ---- tensor-core GEMM --------------------------------------------------------------------------------------------
 // Kernel families (one template instantiation set each).
 enum TcFamily : int { FAM_F16 = 0, FAM_F8 = 1, FAM_I8 = 2, FAM_NVF4 = 3, FAM_W8A16 = 4, FAM_W4A16 = 5, FAM_COUNT = 6 };

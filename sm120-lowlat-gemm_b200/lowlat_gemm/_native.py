@@ -77,6 +77,7 @@ SYMBOLS = {
     "llg_reduce_local": (c_i32, [c_ptr, c_i64, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_ptr, c_i32, c_i32, c_i32, C.c_float, c_i32,
                                  c_ptr]),
     "llg_set_wait_limit": (None, [c_i64]),
+    "llg_sf_relayout": (c_i32, [c_ptr, c_ptr, c_i32, c_i32, c_i64, c_i32, c_ptr]),
     "llg_tc_gemm_host": (c_i32, [C.POINTER(TcArgs), c_ptr, c_ptr, c_i64, c_ptr, c_i64, c_ptr]),
     "llg_device_status": (c_i32, [C.POINTER(C.c_uint32)]),
     "llg_struct_sizes": (None, [C.POINTER(c_i32 * 5)]),

@@ -96,3 +96,19 @@ def test_skinny_order_emulation_is_m_invariant_and_close():
             assert np.array_equal(O.skinny_gemv_exact(x[i:i + 1], w, lpr, ks)[0], y[i])
         ref = x.astype(np.float64) @ w.astype(np.float64).T
         assert np.abs(y - ref).max() < 2e-5 * np.abs(ref).max()
+
+
+def test_block_scale_tiling_is_a_permutation_with_zero_padding():
+    """The tiled block-scale layout of the oracle: every source byte lands exactly once, padding stays zero, the inverse
+    restores the matrix, and the first tile has the published order (row r, column c at (r % 32) * 16 + (r // 32) * 4 + c)."""
+    rng = np.random.default_rng(3)
+    for rows, cols in [(1, 1), (128, 4), (129, 5), (300, 18)]:
+        sf = rng.integers(1, 256, size=(rows, cols), dtype=np.uint8)  # no zeros: padding is recognisable
+        tiled = O.sf_to_tiled(sf)
+        assert tiled.size == -(-rows // 128) * -(-cols // 4) * 512
+        assert np.count_nonzero(tiled) == rows * cols
+        assert np.array_equal(O.sf_from_tiled(tiled, rows, cols), sf)
+    sf = np.arange(128 * 4, dtype=np.uint16).reshape(128, 4).astype(np.uint8)
+    tiled = O.sf_to_tiled(sf)
+    for r, c in [(0, 0), (1, 0), (31, 3), (32, 0), (33, 2), (127, 3)]:
+        assert tiled[(r % 32) * 16 + (r // 32) * 4 + c] == sf[r, c]
