@@ -410,14 +410,15 @@ def run_single(args) -> None:
             in_stream.wait_stream(main)
         else:
             in_stream.wait_event(read_done[i & 1])  # the set's previous contents have been consumed
-        arrived = {}
         with torch.cuda.stream(in_stream):  # inputs come in on their own stream, ahead of the GEMMs that need them
             for m in TOKENS:
                 xs[m].copy_(x_host[m], non_blocking=True)
-                arrived[m] = in_stream.record_event()
+            arrived = in_stream.record_event()
+        # one join per step: a cross-stream edge in front of every quantizer would turn each of them into a full
+        # (not programmatic) dependency of the GEMM before it
+        main.wait_event(arrived)
         for m in TOKENS:
             w, kw = weights()
-            main.wait_event(arrived[m])
             q, s = L.quantize_fp8(xs[m])
             if m == TOKENS[-1]:
                 read_done[i & 1] = main.record_event()
