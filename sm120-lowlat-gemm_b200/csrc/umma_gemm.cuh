@@ -137,6 +137,54 @@ __device__ __forceinline__ void tc_store(const TcDev& prm, int p, int q, float v
     if (d < prm.push_n) tc_store_to(prm.push_y[d], prm.out_dtype, at, v);
 }
 
+// Column-side factors of 16 consecutive columns: scale (1 when absent) and bias as fp32 (0 when absent or indexed by
+// p). The kind of vector is decided once per call, so the 16 loads are straight-line code: the epilogue runs as one
+// warp per scheduler with nothing to hide a branch behind.
+__device__ __forceinline__ void tc_col_factors(const TcDev& prm, int q_first, float (&cs)[16], float (&cb)[16]) {
+  const int last = prm.Q - 1;
+  if (prm.col_scale_len > 1) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) cs[c] = __ldg(prm.col_scale + min(q_first + c, last));
+  } else {
+    const float one = prm.col_scale_len == 1 ? __ldg(prm.col_scale) : 1.f;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) cs[c] = one;
+  }
+  if (prm.bias_dtype == LLG_DT_NONE || prm.bias_on_p) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) cb[c] = 0.f;
+  } else if (prm.bias_dtype == LLG_DT_BF16) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) cb[c] = __bfloat162float(static_cast<const __nv_bfloat16*>(prm.bias)[min(q_first + c, last)]);
+  } else if (prm.bias_dtype == LLG_DT_F16) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) cb[c] = __half2float(static_cast<const __half*>(prm.bias)[min(q_first + c, last)]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) cb[c] = __ldg(static_cast<const float*>(prm.bias) + min(q_first + c, last));
+  }
+}
+
+__device__ __forceinline__ void tc_put(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void tc_put(__half* p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void tc_put(float* p, float v) { *p = v; }
+
+// 16 finished values of one accumulator row, stored transposed: element c goes to y[q_first + c][p] (the lanes of a
+// warp hold consecutive p, so every store instruction writes one contiguous run).
+template <typename T>
+__device__ __forceinline__ void tc_emit_transposed(void* y, int64_t ldy, int p, int q_first, int nvalid, const float (&o)[16]) {
+  T* const dst = static_cast<T*>(y) + (int64_t)q_first * ldy + p;
+#pragma unroll
+  for (int c = 0; c < 16; ++c)
+    if (c < nvalid) tc_put(dst + (int64_t)c * ldy, o[c]);
+}
+__device__ __forceinline__ void tc_emit_transposed_any(void* y, int out_dtype, int64_t ldy, int p, int q_first, int nvalid,
+                                                       const float (&o)[16]) {
+  if (out_dtype == LLG_DT_BF16) tc_emit_transposed<__nv_bfloat16>(y, ldy, p, q_first, nvalid, o);
+  else if (out_dtype == LLG_DT_F16) tc_emit_transposed<__half>(y, ldy, p, q_first, nvalid, o);
+  else tc_emit_transposed<float>(y, ldy, p, q_first, nvalid, o);
+}
+
 // ---- exact widening of 8-bit / 4-bit floats to 16-bit pairs ---------------------------------------------------------
 
 // four e4m3 bytes -> (k0,k1) and (k2,k3) as bf16x2 / f16x2
@@ -811,16 +859,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (prm.bias_dtype != LLG_DT_NONE && prm.bias_on_p) bias_p = tc_bias(prm, p);
       }
       // ... and so are the column-side factors of the first 16 columns (all of them for decode-sized tiles)
-      const bool col_bias = prm.bias_dtype != LLG_DT_NONE && !prm.bias_on_p;
-      float cs0[16], cb0[16];
-      if (ksplit == 1 && row_ok) {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int q = q0 + c < prm.Q ? q0 + c : prm.Q - 1;
-          cs0[c] = tc_vec(prm.col_scale, prm.col_scale_len, q);
-          cb0[c] = col_bias ? tc_bias(prm, q) : 0.f;
-        }
-      }
+      const bool has_bias = prm.bias_dtype != LLG_DT_NONE, bias_on_p = prm.bias_on_p != 0;
+      float csn[16], cbn[16];  // factors of the chunk about to be processed, always fetched one chunk ahead
+      if (ksplit == 1 && row_ok) tc_col_factors(prm, q0, csn, cbn);
       if (w.ntiles > 0) {
         if (ok) {
           ok = mbar_wait(smem_u32(&hdr->acc_full[ab]), (n_acc / G::kAccBufs) & 1, abort_word);
@@ -851,62 +892,62 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (ksplit == 1) {
           if (row_ok) {
-            // column-side factors of the whole chunk first (independent loads in flight together), then the stores
-            float cs[16], cb[16];
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              if (c0 == 0) {  // fetched before the accumulator wait
-                cs[c] = cs0[c];
-                cb[c] = cb0[c];
-              } else {
-                const int q = q0 + c0 + c < prm.Q ? q0 + c0 + c : prm.Q - 1;
-                cs[c] = tc_vec(prm.col_scale, prm.col_scale_len, q);
-                cb[c] = col_bias ? tc_bias(prm, q) : 0.f;
-              }
-            }
             float o[16];
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
               const float acc = G::kIntAcc ? (float)(int32_t)v[c] : __uint_as_float(v[c]);
-              float t = __fmul_rn(__fmul_rn(__fmul_rn(acc, alpha), rs), cs[c]);
-              if (prm.bias_dtype != LLG_DT_NONE) t = __fadd_rn(t, prm.bias_on_p ? bias_p : cb[c]);
-              o[c] = t;
+              const float t = __fmul_rn(__fmul_rn(__fmul_rn(acc, alpha), rs), csn[c]);
+              o[c] = has_bias ? __fadd_rn(t, bias_on_p ? bias_p : cbn[c]) : t;
             }
-            bool done = false;
-            if (!prm.swap && c0 + 16 <= nq && prm.push_n == 0) {
-              // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
-              if (prm.out_dtype == LLG_DT_F32) {
-                float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
-                if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-                  for (int c = 0; c < 16; c += 4)
-                    *reinterpret_cast<float4*>(dst + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-                  done = true;
-                }
+            // the next chunk's factors travel while this chunk is stored
+            if (c0 + 16 < nq) tc_col_factors(prm, q0 + c0 + 16, csn, cbn);
+            const int nvalid = min(16, nq - c0);
+            if (prm.swap) {
+              if (prm.push_n == 0) {
+                tc_emit_transposed_any(prm.y, prm.out_dtype, prm.ldy, p, q0 + c0, nvalid, o);
               } else {
-                uint16_t* dst = static_cast<uint16_t*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
-                if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                  uint32_t w2[8];
+                // push mode: to every rank's copy of this rank's partial (plain stores into peer-mapped memory)
 #pragma unroll
-                  for (int c = 0; c < 16; c += 2) {
-                    if (prm.out_dtype == LLG_DT_BF16) {
-                      const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(o[c]), __float2bfloat16_rn(o[c + 1]));
-                      w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
-                    } else {
-                      const __half2 t = __halves2half2(__float2half_rn(o[c]), __float2half_rn(o[c + 1]));
-                      w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
-                    }
+                for (int d = 0; d < 8; ++d)
+                  if (d < prm.push_n) tc_emit_transposed_any(prm.push_y[d], prm.out_dtype, prm.ldy, p, q0 + c0, nvalid, o);
+              }
+            } else {
+              bool done = false;
+              if (nvalid == 16 && prm.push_n == 0) {
+                // 16 consecutive outputs of one row: vector stores when the run is 16-byte aligned
+                if (prm.out_dtype == LLG_DT_F32) {
+                  float* dst = static_cast<float*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
+                  if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                    for (int c = 0; c < 16; c += 4)
+                      *reinterpret_cast<float4*>(dst + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                    done = true;
                   }
-                  *reinterpret_cast<uint4*>(dst) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
-                  *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w2[4], w2[5], w2[6], w2[7]);
-                  done = true;
+                } else {
+                  uint16_t* dst = static_cast<uint16_t*>(prm.y) + (int64_t)p * prm.ldy + q0 + c0;
+                  if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    uint32_t w2[8];
+#pragma unroll
+                    for (int c = 0; c < 16; c += 2) {
+                      if (prm.out_dtype == LLG_DT_BF16) {
+                        const __nv_bfloat162 t = __halves2bfloat162(__float2bfloat16_rn(o[c]), __float2bfloat16_rn(o[c + 1]));
+                        w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                      } else {
+                        const __half2 t = __halves2half2(__float2half_rn(o[c]), __float2half_rn(o[c + 1]));
+                        w2[c / 2] = *reinterpret_cast<const uint32_t*>(&t);
+                      }
+                    }
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+                    *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w2[4], w2[5], w2[6], w2[7]);
+                    done = true;
+                  }
                 }
               }
-            }
-            if (!done) {
+              if (!done) {
 #pragma unroll
-              for (int c = 0; c < 16; ++c)
-                if (c0 + c < nq) tc_store(prm, p, q0 + c0 + c, o[c]);
+                for (int c = 0; c < 16; ++c)
+                  if (c < nvalid) tc_store(prm, p, q0 + c0 + c, o[c]);
+              }
             }
           }
         } else if (prm.cluster) {

@@ -435,7 +435,7 @@ def test_supports_and_shapes():
     with pytest.raises(ValueError):
         L.gemm(x[:, :32], w)
     with pytest.raises(RuntimeError, match="lowlat_gemm:"):
-        torch.ops.lowlat_gemm.tc_gemm(out, x, w, None, None, None, None, None, None, 1.0, 0, False, False, 11, 2, 1,
+        torch.ops.lowlat_gemm.tc_gemm(out, x, w, None, None, None, None, None, None, 1.0, 0, False, False, L.NUM_CFGS, 2, 1,
                                       *L._workspace(torch.device(DEV), 0, 0))
 
 
