@@ -176,7 +176,7 @@ int tc_family_of(int kind);
 // bytes per stage of (family, cfg); 0 if invalid
 int tc_stage_bytes_of(int kind, int cfg);
 int tc_threads_of(int kind);  // 192, or 320 for the kinds with helper warps (block scales / widening)
-constexpr int kSmemBudget = 227 * 1024 - 2048;  // dynamic shared memory for stages; the rest holds barriers and slack
+constexpr int kSmemBudget = 227 * 1024 - 3072;  // dynamic shared memory for stages; the rest holds the header (barriers, epilogue factors) and alignment slack
 
 // 256-row tiles on CTA pairs (umma_pair.cu): families F16, F8 and I8, bq 128 or 256, no split-K.
 cudaError_t tc_launch_pair(int family, const CUtensorMap& ta, const CUtensorMap& tb, const TcDev& p, int bq, bool pdl, cudaStream_t s);

@@ -31,7 +31,7 @@ namespace llg {
 constexpr int kBP = 128;
 constexpr int kAtomBytes = 128;           // bytes of K per row in one swizzle atom
 constexpr int kAAtomTile = kBP * 128;     // one A atom tile in shared memory
-constexpr int kHeaderBytes = 1024;
+constexpr int kHeaderBytes = 2048;
 constexpr int kSfLag = 3;                 // block-scale cp.async groups kept in flight per thread
 
 template <int FAM, int BQ, int ATOMS>
@@ -84,6 +84,9 @@ struct SmemHeader {
   uint32_t last;
   uint32_t trace_slot;
   uint32_t prod_stage;               // first item: stages the producer has issued (0 until the dependency resolved)
+  // column-side epilogue factors (scale, bias as fp32) of the tile in flight, tiles up to 64 columns wide; two sets,
+  // so that the fetch for the next item never overwrites what a slower epilogue warp still reads
+  alignas(16) float colf[2][2][64];
 };
 static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header too large");
 
@@ -163,6 +166,14 @@ __device__ __forceinline__ void tc_col_factors(const TcDev& prm, int q_first, fl
 #pragma unroll
     for (int c = 0; c < 16; ++c) cb[c] = __ldg(static_cast<const float*>(prm.bias) + min(q_first + c, last));
   }
+}
+
+// The same two factors for one column (scale in .x, bias in .y).
+__device__ __forceinline__ float2 tc_col_factor(const TcDev& prm, int q) {
+  float2 f;
+  f.x = tc_vec(prm.col_scale, prm.col_scale_len, q);
+  f.y = (prm.bias_dtype != LLG_DT_NONE && !prm.bias_on_p) ? tc_bias(prm, q) : 0.f;
+  return f;
 }
 
 __device__ __forceinline__ void tc_put(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
@@ -860,8 +871,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       // ... and so are the column-side factors of the first 16 columns (all of them for decode-sized tiles)
       const bool has_bias = prm.bias_dtype != LLG_DT_NONE, bias_on_p = prm.bias_on_p != 0;
-      float csn[16], cbn[16];  // factors of the chunk about to be processed, always fetched one chunk ahead
-      if (ksplit == 1 && row_ok) tc_col_factors(prm, q0, csn, cbn);
+      // Column factors. Tiles up to 64 columns wide: the epilogue threads fetch the whole tile's factors into shared
+      // memory now (one column each) and every chunk reads them from there. Wider tiles: registers, one chunk ahead.
+      float csn[16], cbn[16];
+      float* const cs_s = hdr->colf[n_acc & 1u][0];
+      float* const cb_s = hdr->colf[n_acc & 1u][1];
+      if constexpr (BQ <= 64) {
+        if (ksplit == 1) {
+          if (et < BQ) {
+            const float2 f = tc_col_factor(prm, q0 + et < prm.Q ? q0 + et : prm.Q - 1);
+            cs_s[et] = f.x;
+            cb_s[et] = f.y;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      } else {
+        if (ksplit == 1 && row_ok) tc_col_factors(prm, q0, csn, cbn);
+      }
       if (w.ntiles > 0) {
         if (ok) {
           ok = mbar_wait(smem_u32(&hdr->acc_full[ab]), (n_acc / G::kAccBufs) & 1, abort_word);
@@ -892,6 +918,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (ksplit == 1) {
           if (row_ok) {
+            if constexpr (BQ <= 64) {
+#pragma unroll
+              for (int c = 0; c < 16; c += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(cs_s + c0 + c), b = *reinterpret_cast<const float4*>(cb_s + c0 + c);
+                csn[c] = a.x; csn[c + 1] = a.y; csn[c + 2] = a.z; csn[c + 3] = a.w;
+                cbn[c] = b.x; cbn[c + 1] = b.y; cbn[c + 2] = b.z; cbn[c + 3] = b.w;
+              }
+            }
             float o[16];
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
@@ -900,7 +934,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o[c] = has_bias ? __fadd_rn(t, bias_on_p ? bias_p : cbn[c]) : t;
             }
             // the next chunk's factors travel while this chunk is stored
-            if (c0 + 16 < nq) tc_col_factors(prm, q0 + c0 + 16, csn, cbn);
+            if constexpr (BQ > 64) {
+              if (c0 + 16 < nq) tc_col_factors(prm, q0 + c0 + 16, csn, cbn);
+            }
             const int nvalid = min(16, nq - c0);
             if (prm.swap) {
               if (prm.push_n == 0) {
