@@ -92,15 +92,19 @@ static_assert(sizeof(SmemHeader) <= kHeaderBytes, "header too large");
 
 __device__ __forceinline__ void give_up(const TcDev& prm, uint32_t code) { atomicCAS(prm.status, 0u, code); }
 
+// Element i of a scale vector that may be absent (1), a scalar or a full vector. Written as selects and a predicated
+// load rather than branches: the epilogue runs as one warp per scheduler, where a branch is paid in full.
 __device__ __forceinline__ float tc_vec(const float* p, int len, int i) {
-  return len == 0 ? 1.f : (len == 1 ? __ldg(p) : __ldg(p + i));
+  const float* const at = p + (len > 1 ? i : 0);
+  return len == 0 ? 1.f : __ldg(at);
 }
 __device__ __forceinline__ float tc_bias(const TcDev& prm, int i) {
-  switch (prm.bias_dtype) {
-    case LLG_DT_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(prm.bias)[i]);
-    case LLG_DT_F16: return __half2float(static_cast<const __half*>(prm.bias)[i]);
-    default: return static_cast<const float*>(prm.bias)[i];
-  }
+  const bool wide = prm.bias_dtype == LLG_DT_F32;
+  const float f = wide ? __ldg(static_cast<const float*>(prm.bias) + i) : 0.f;
+  const unsigned short h = wide ? (unsigned short)0 : __ldg(static_cast<const unsigned short*>(prm.bias) + i);
+  const float from_bf16 = __uint_as_float((uint32_t)h << 16);
+  const float from_f16 = __half2float(__ushort_as_half(h));
+  return wide ? f : (prm.bias_dtype == LLG_DT_BF16 ? from_bf16 : from_f16);
 }
 
 // v = ((acc * alpha) * row_scale[p]) * col_scale[q] (+ bias), every operation individually rounded.
@@ -121,11 +125,10 @@ __device__ __forceinline__ float tc_finish_row(const TcDev& prm, float alpha, fl
   return v;
 }
 __device__ __forceinline__ void tc_store_to(void* y, int out_dtype, int64_t at, float v) {
-  switch (out_dtype) {
-    case LLG_DT_BF16: static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v); break;
-    case LLG_DT_F16: static_cast<__half*>(y)[at] = __float2half_rn(v); break;
-    default: static_cast<float*>(y)[at] = v; break;
-  }
+  // three predicated stores of which one executes (the type is uniform over the grid)
+  if (out_dtype == LLG_DT_BF16) static_cast<__nv_bfloat16*>(y)[at] = __float2bfloat16_rn(v);
+  if (out_dtype == LLG_DT_F16) static_cast<__half*>(y)[at] = __float2half_rn(v);
+  if (out_dtype == LLG_DT_F32) static_cast<float*>(y)[at] = v;
 }
 // One finished output element. In push mode it goes to every rank's copy of this rank's partial (plain stores into
 // peer-mapped memory; the transfer so overlaps the tiles that are still being computed) instead of to y.
@@ -1081,22 +1084,43 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int np = min(kBP, prm.P - w.p0), nq = min(BQ, prm.Q - w.q0);
       const int total = kBP * nq, share = (total + ksplit - 1) / ksplit;
       const int lo = (int)cluster_ctarank() * share, hi = min(total, lo + share);
-      for (int i = lo + et; i < hi; i += 128) {
-        const int pl = i % kBP, ql = i / kBP;
-        if (pl >= np) continue;
-        const uint32_t addr = stage0 + (uint32_t)i * 4u;
-        uint32_t part[8];
+      const bool has_bias = prm.bias_dtype != LLG_DT_NONE;
+      for (int i0 = lo + et; i0 < hi; i0 += 4 * 128) {
+        // four elements per thread at a time: every partial and every epilogue factor of the batch is requested before
+        // the first sum, so the distributed-shared-memory and global latencies overlap instead of adding up
+        uint32_t part[4][8];
+        float rs[4], cs[4], bv[4];
+        int pp[4], qq[4];
+        bool live[4];
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          if (k < ksplit) part[k] = ld_cluster_u32(cluster_map_shared(addr, (uint32_t)k));
-        uint32_t sum = part[0];
+        for (int e = 0; e < 4; ++e) {
+          const int i = i0 + e * 128;
+          const int pl = i % kBP, ql = i / kBP;
+          live[e] = i < hi && pl < np;
+          pp[e] = w.p0 + (live[e] ? pl : 0);
+          qq[e] = w.q0 + (live[e] ? ql : 0);
+          const uint32_t addr = stage0 + (uint32_t)(live[e] ? i : lo) * 4u;
 #pragma unroll
-        for (int k = 1; k < 8; ++k)
-          if (k < ksplit) {
-            if constexpr (G::kIntAcc) sum = (uint32_t)((int32_t)sum + (int32_t)part[k]);
-            else sum = __float_as_uint(__uint_as_float(sum) + __uint_as_float(part[k]));
-          }
-        tc_store(prm, w.p0 + pl, w.q0 + ql, tc_finish<G::kIntAcc>(prm, alpha, w.p0 + pl, w.q0 + ql, sum));
+          for (int k = 0; k < 8; ++k)
+            if (k < ksplit) part[e][k] = ld_cluster_u32(cluster_map_shared(addr, (uint32_t)k));
+          rs[e] = tc_vec(prm.row_scale, prm.row_scale_len, pp[e]);
+          cs[e] = tc_vec(prm.col_scale, prm.col_scale_len, qq[e]);
+          bv[e] = has_bias ? tc_bias(prm, prm.bias_on_p ? pp[e] : qq[e]) : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          uint32_t sum = part[e][0];
+#pragma unroll
+          for (int k = 1; k < 8; ++k)
+            if (k < ksplit) {  // added in split order
+              if constexpr (G::kIntAcc) sum = (uint32_t)((int32_t)sum + (int32_t)part[e][k]);
+              else sum = __float_as_uint(__uint_as_float(sum) + __uint_as_float(part[e][k]));
+            }
+          const float acc = G::kIntAcc ? (float)(int32_t)sum : __uint_as_float(sum);
+          const float t = __fmul_rn(__fmul_rn(__fmul_rn(acc, alpha), rs[e]), cs[e]);
+          const float v = has_bias ? __fadd_rn(t, bv[e]) : t;
+          if (live[e]) tc_store(prm, pp[e], qq[e], v);
+        }
       }
     }
     cluster_arrive();  // partials stay readable until every CTA of the cluster is done with them

@@ -228,6 +228,52 @@ def test_tiles_on_cta_pairs(kind):
     no_expired_wait()
 
 
+def test_pair_tiles_in_a_pdl_chain_and_graph():
+    """Three dependent GEMMs on pair tiles (the middle one between two single-CTA launches' worth of rows), eagerly
+    with and without programmatic dependent launch and from a replayed CUDA graph with poisoned outputs: same bits."""
+    g = torch.Generator().manual_seed(11)
+    m, dims = 384, [1024, 2048, 768, 1536]
+    ws = [(torch.randn(dims[i + 1], dims[i], generator=g) / dims[i] ** 0.5).to(torch.bfloat16).to(DEV) for i in range(3)]
+    plans = [Plan(tc={m: TcChoice(cfg=11, swap=False, stages=6)}), Plan(tc={m: TcChoice(cfg=10, swap=True, stages=3)}),
+             Plan(tc={m: TcChoice(cfg=11, swap=False, stages=2)})]
+    x = torch.randn(m, dims[0], generator=g).to(torch.bfloat16).to(DEV)
+    outs = [torch.empty(m, d, device=DEV, dtype=torch.bfloat16) for d in dims[1:]]
+
+    def chain():
+        h = x
+        for w, p, o in zip(ws, plans, outs):
+            L.gemm(h, w, out=o, plan=p)
+            h = o
+
+    L.set_pdl(False)
+    chain()
+    ref = [o.clone() for o in outs]
+    want = x.double() @ ws[0].double().T
+    assert rel_err(ref[0].double(), want.cpu().numpy()) < 1e-2  # bf16 output of a correct product
+    try:
+        L.set_pdl(True)
+        chain()
+        assert all(torch.equal(o, r) for o, r in zip(outs, ref))
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            chain()
+        torch.cuda.current_stream().wait_stream(s)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(3):
+                chain()
+        for _ in range(10):
+            for o in outs:
+                o.fill_(float("nan"))
+            graph.replay()
+            torch.cuda.synchronize()
+            assert all(torch.equal(o, r) for o, r in zip(outs, ref))
+    finally:
+        L.set_pdl(False)
+    no_expired_wait()
+
+
 @pytest.mark.parametrize("kind", ALL_KINDS)
 def test_deep_pipelines(kind):
     m, n, k = 5, 72, 24 * 256
