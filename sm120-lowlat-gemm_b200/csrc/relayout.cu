@@ -3,7 +3,7 @@
 // tiles of 128 rows x 4 scale columns, 512 contiguous bytes each, the byte of (row r, column c) of a tile at
 // (r % 32) * 16 + (r / 32) * 4 + c, tiles ordered row tile major with rows and columns padded to whole tiles.
 // Pure byte movement, HBM-bound: one CTA moves a 128-row x 128-column block through shared memory so that both the
-// reads and the writes are contiguous.
+// reads and the writes are contiguous (the tiled buffer needs 16-byte alignment, hence whole words on that side).
 #include "llg_internal.h"
 
 namespace llg {
@@ -13,56 +13,55 @@ namespace {
 constexpr int kTileRows = 128, kTileCols = 4, kTileBytes = 512;
 constexpr int kTilesPerCta = 32;  // 128 scale columns per CTA
 
-__device__ __forceinline__ int tiled_at(int r, int c) { return (r & 31) * 16 + (r >> 5) * 4 + c; }
+constexpr int kTileWords = kTileBytes / 4, kTilePitch = kTileWords + 1;  // +1 word: a warp's 32 tiles fall on 32 banks
 
 __global__ void __launch_bounds__(256) sf_relayout_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
                                                           int rows, int cols, int64_t ld, int to_tiled, int words) {
-  __shared__ __align__(16) unsigned char buf[kTilesPerCta * kTileBytes];  // tiled order
+  // tiles in tiled word order, one padding word between tiles: the row-major side walks a row across the tiles
+  // (word (r % 32) * 4 + r / 32 of every tile), the tiled side walks the words of a tile
+  __shared__ uint32_t buf[kTilesPerCta * kTilePitch];
   const int col_tiles = (cols + kTileCols - 1) / kTileCols;
   const int rt = blockIdx.y, ct0 = blockIdx.x * kTilesPerCta;
   const int nt = min(kTilesPerCta, col_tiles - ct0);
-  const int64_t tiled_off = ((int64_t)rt * col_tiles + ct0) * kTileBytes;
-  unsigned char* const lin_dst = dst;
+  const int64_t tiled_word0 = ((int64_t)rt * col_tiles + ct0) * kTileWords;
   if (to_tiled) {
-    // row-major -> shared memory (tiled order); bytes outside the matrix become zero
+    // row-major -> shared memory; bytes outside the matrix become zero
     for (int i = threadIdx.x; i < kTileRows * nt; i += blockDim.x) {
       const int r = i / nt, t = i - r * nt;  // consecutive threads: consecutive 4-byte groups of one row
       const int64_t row = (int64_t)rt * kTileRows + r;
       const int c0 = (ct0 + t) * kTileCols;
-      unsigned char v[4] = {0, 0, 0, 0};
+      uint32_t v = 0u;
       if (row < rows) {
         if (words && c0 + 4 <= cols) {  // rows are 4-byte aligned: one load
-          const uchar4 w = *reinterpret_cast<const uchar4*>(src + row * ld + c0);
-          v[0] = w.x; v[1] = w.y; v[2] = w.z; v[3] = w.w;
+          v = *reinterpret_cast<const uint32_t*>(src + row * ld + c0);
         } else {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            if (c0 + c < cols) v[c] = src[row * ld + c0 + c];
+            if (c0 + c < cols) v |= (uint32_t)src[row * ld + c0 + c] << (8 * c);
         }
       }
-      *reinterpret_cast<uchar4*>(buf + t * kTileBytes + tiled_at(r, 0)) = make_uchar4(v[0], v[1], v[2], v[3]);
+      buf[t * kTilePitch + (r & 31) * 4 + (r >> 5)] = v;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < nt * kTileBytes / 16; i += blockDim.x)
-      reinterpret_cast<uint4*>(dst + tiled_off)[i] = reinterpret_cast<const uint4*>(buf)[i];
+    uint32_t* const out = reinterpret_cast<uint32_t*>(dst) + tiled_word0;
+    for (int i = threadIdx.x; i < nt * kTileWords; i += blockDim.x) out[i] = buf[(i / kTileWords) * kTilePitch + i % kTileWords];
   } else {
-    for (int i = threadIdx.x; i < nt * kTileBytes / 16; i += blockDim.x)
-      reinterpret_cast<uint4*>(buf)[i] = reinterpret_cast<const uint4*>(src + tiled_off)[i];
+    const uint32_t* const in = reinterpret_cast<const uint32_t*>(src) + tiled_word0;
+    for (int i = threadIdx.x; i < nt * kTileWords; i += blockDim.x) buf[(i / kTileWords) * kTilePitch + i % kTileWords] = in[i];
     __syncthreads();
     for (int i = threadIdx.x; i < kTileRows * nt; i += blockDim.x) {
       const int r = i / nt, t = i - r * nt;
       const int64_t row = (int64_t)rt * kTileRows + r;
       if (row >= rows) continue;
-      const uchar4 v = *reinterpret_cast<const uchar4*>(buf + t * kTileBytes + tiled_at(r, 0));
-      const unsigned char b[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t v = buf[t * kTilePitch + (r & 31) * 4 + (r >> 5)];
       const int c0 = (ct0 + t) * kTileCols;
       if (words && c0 + 4 <= cols) {
-        *reinterpret_cast<uchar4*>(lin_dst + row * ld + c0) = v;
+        *reinterpret_cast<uint32_t*>(dst + row * ld + c0) = v;
         continue;
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c)
-        if (c0 + c < cols) lin_dst[row * ld + c0 + c] = b[c];
+        if (c0 + c < cols) dst[row * ld + c0 + c] = (unsigned char)(v >> (8 * c));
     }
   }
 }

@@ -3,6 +3,8 @@
     python -m lowlat_gemm.profile_case gemm  --kind fp8 --n 14336 --k 4096 --m 16 [--engine tc|skinny|plan] [--calls 8]
     python -m lowlat_gemm.profile_case quant --mode fp8|int8|nvfp4|gated_fp8 --m 8 --k 8192
     python -m lowlat_gemm.profile_case step  --kind fp8 --tokens 8 --layers 2        (one-GPU decode step, push form)
+    python -m lowlat_gemm.profile_case allreduce --rows 8 --cols 8192                (pull-form kernels, one rank on local memory)
+    python -m lowlat_gemm.profile_case relayout --rows 28672 --cols 512              (block-scale layout converter)
 
 Every call of `gemm` reads a different copy of the weight and the copies together exceed the L2 cache, so DRAM counters
 mean what they mean in a decode step, while the whole case holds well under 2 GB on the device and launches only a
@@ -74,6 +76,38 @@ def run_step(a) -> None:
     print(f"decode step {a.kind} tokens={a.tokens} layers={a.layers}: finite={bool(torch.isfinite(y.float()).all())}")
 
 
+def run_allreduce(a) -> None:
+    """The pull-form kernels with a single rank on ordinary device memory: same code path as with peers (flag
+    handshake with itself, rank-order sum of one partial), so a one-GPU capture shows their fixed costs."""
+    from lowlat_gemm import comm as CM
+    dev = torch.device("cuda", 0)
+    ar = CM.OneShotAllReduce(None, dev, max_bytes=a.rows * a.cols * 2, local=True)
+    g = torch.Generator(device=dev).manual_seed(2)
+    out = torch.empty(a.rows, a.cols, device=dev, dtype=torch.bfloat16)
+    for i in range(a.calls):
+        ar.view(i, (a.rows, a.cols), torch.bfloat16).copy_(torch.randn(a.rows, a.cols, device=dev, generator=g).to(torch.bfloat16))
+        if i % 2:
+            ar.reduce_quantize_fp8(i, a.rows, a.cols, torch.bfloat16, out=out)
+        else:
+            ar.reduce(i, out)
+    torch.cuda.synchronize()
+    print(f"all-reduce (pull form, one rank) [{a.rows}, {a.cols}]: {a.calls} calls, |out| sum {float(out.float().abs().sum()):.4g}")
+
+
+def run_relayout(a) -> None:
+    from lowlat_gemm import convert as CV
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(3)
+    sfs = [torch.randint(0, 256, (a.rows, a.cols), device=dev, generator=g, dtype=torch.uint8) for _ in range(4)]
+    ok = True
+    for i in range(a.calls):
+        tiled = CV.scales_to_tiled(sfs[i % 4])
+        back = CV.scales_to_rowmajor(tiled, a.rows, a.cols)
+        ok = ok and bool(torch.equal(back.view(torch.uint8), sfs[i % 4]))
+    torch.cuda.synchronize()
+    print(f"scale relayout [{a.rows}, {a.cols}]: {a.calls} round trips, restored={ok}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
@@ -96,8 +130,16 @@ def main() -> None:
     s.add_argument("--tokens", type=int, default=8)
     s.add_argument("--layers", type=int, default=2)
     s.add_argument("--pdl", action="store_true")
+    r = sub.add_parser("allreduce")
+    r.add_argument("--rows", type=int, default=8)
+    r.add_argument("--cols", type=int, default=8192)
+    r.add_argument("--calls", type=int, default=8)
+    t = sub.add_parser("relayout")
+    t.add_argument("--rows", type=int, default=28672)
+    t.add_argument("--cols", type=int, default=512)
+    t.add_argument("--calls", type=int, default=6)
     a = ap.parse_args()
-    {"gemm": run_gemm, "quant": run_quant, "step": run_step}[a.what](a)
+    {"gemm": run_gemm, "quant": run_quant, "step": run_step, "allreduce": run_allreduce, "relayout": run_relayout}[a.what](a)
 
 
 if __name__ == "__main__":
