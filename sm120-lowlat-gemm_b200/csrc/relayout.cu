@@ -2,7 +2,7 @@
 // ([rows, K/16] bytes) and the tiled form in which checkpoints prepared for block-scaled tensor-core GEMMs store them:
 // tiles of 128 rows x 4 scale columns, 512 contiguous bytes each, the byte of (row r, column c) of a tile at
 // (r % 32) * 16 + (r / 32) * 4 + c, tiles ordered row tile major with rows and columns padded to whole tiles.
-// Pure byte movement, HBM-bound: one CTA moves a 128-row x 128-column block through shared memory so that both the
+// Pure byte movement, run once per weight at load time: one CTA moves a 128-row x 128-column block through shared memory so that both the
 // reads and the writes are contiguous (the tiled buffer needs 16-byte alignment, hence whole words on that side).
 #include "llg_internal.h"
 
