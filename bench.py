@@ -53,8 +53,8 @@ def peaks() -> dict:
     f = ROOT / "MEASURED_PEAKS.json"
     if f.is_file():
         d = json.loads(f.read_text())
-        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "source": "fallback"}
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 1590.0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -268,7 +268,7 @@ def kind_rows(dev, pk: dict) -> list:
     rotating weight copies, median of five replays), achieved GB/s from the algorithmic bytes, fraction of the measured
     copy bandwidth."""
     import lowlat_gemm as L
-    from lowlat_gemm import timing
+    from lowlat_gemm import api, timing
     rows = []
     for kind, n, k in KIND_ROWS:
         cold = timing.ColdWeights(kind, n, k, dev)
@@ -285,6 +285,21 @@ def kind_rows(dev, pk: dict) -> list:
             engine = "skinny" if plan.skinny is not None and m <= min(plan.skinny_max_m, 16) else "tcgen05"
             rows.append({"kind": kind, "n": n, "k": k, "m": m, "us": us, "gbs": gbs, "frac": gbs / pk["hbm_gbs"],
                          "pct_of_8tbs": gbs / 80.0, "engine": engine})
+        del cold
+        torch.cuda.empty_cache()
+    # the tensor-bound end of the same entry point: hundreds to thousands of token rows (256-row tiles on CTA pairs);
+    # bf16 against the measured cuBLAS bf16 rate, fp8 against the nominal dense rate (no measured figure exists)
+    for kind, n, k, peak, peak_name in (("bf16", 11008, 4096, pk["bf16_tflops"], "measured cuBLAS bf16 burst"),
+                                        ("fp8", 14336, 4096, 4500.0, "nominal dense fp8")):
+        cold = timing.ColdWeights(kind, n, k, dev)
+        for m in (256, 2048):
+            x, x_kw = timing.make_input(kind, m, k, dev)
+            out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+            us = timing.time_per_call(lambda w, kw, nxt: L.gemm(x, w, out=out, **kw, **x_kw), cold, calls=16, replays=5)
+            tf = 2.0 * m * n * k / us / 1e6
+            choice = api.tc_choice_for(kind, m, n, k, L.get_plan(kind, n, k, dev), dev)
+            rows.append({"kind": kind, "n": n, "k": k, "m": m, "us": us, "tflops": tf, "bound": "tensor", "peak_tflops": peak,
+                         "peak": peak_name, "frac": tf / peak, "engine": "tcgen05 cta_group::2" if choice.cfg in L.PAIR_CFGS else "tcgen05"})
         del cold
         torch.cuda.empty_cache()
     return rows
