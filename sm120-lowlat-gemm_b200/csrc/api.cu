@@ -195,7 +195,7 @@ int tc_family_of(int kind) {
 
 int tc_threads_of(int kind) {
   const int f = tc_family_of(kind);
-  return f == FAM_W4A16 ? 192 + 512 : f == FAM_W8A16 ? 192 + 256 : f == FAM_NVF4 ? 320 : 192;
+  return f == FAM_W4A16 ? 192 + 256 : f == FAM_W8A16 ? 192 + 256 : f == FAM_NVF4 ? 320 : 192;
 }
 
 int tc_stage_bytes_of(int kind, int cfg) {

@@ -175,7 +175,7 @@ TcTile tc_tile_of(int cfg);
 int tc_family_of(int kind);
 // bytes per stage of (family, cfg); 0 if invalid
 int tc_stage_bytes_of(int kind, int cfg);
-int tc_threads_of(int kind);  // 192, or 320 for the kinds with helper warps (block scales / widening)
+int tc_threads_of(int kind);  // 192; 320 with NVFP4's block-scale feeders; 448 with the mixed kinds' converter warps
 constexpr int kSmemBudget = 227 * 1024 - 3072;  // dynamic shared memory for stages; the rest holds the header (barriers, epilogue factors) and alignment slack
 
 // 256-row tiles on CTA pairs (umma_pair.cu): families F16, F8 and I8, bq 128 or 256, no split-K.

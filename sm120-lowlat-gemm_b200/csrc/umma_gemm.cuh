@@ -6,7 +6,7 @@
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, scale / bias / convert / store, split-K reduction; while it
 //               has nothing to do, one of them asks for the CTA's later weight stages to be brought into L2
 //   warps 6-    helpers, only for some kinds: NVFP4 - four warps put the block scales of every stage into the layout
-//               the MMA's scale copy reads; W8A16 / W4A16 - 8 / 16 warps widen the weight tile exactly into tensor
+//               the MMA's scale copy reads; W8A16 / W4A16 - 8 warps widen the weight tile exactly into tensor
 //               memory (the MMA then takes A from there), in two groups that take alternate stages
 // The host maps (activation, weight) onto (A, B): with few tokens the weight is A ("swap": its rows fill the 128
 // MMA rows, the tokens sit on the narrow N side and y is stored transposed).
@@ -41,7 +41,7 @@ struct Geo {
   static constexpr bool kIntAcc = FAM == FAM_I8;
   static constexpr bool kHelpers = kMixed || kNvf4;              // warps 6..: converter / block-scale feeder
   // helper threads per tile row: the widening is ALU work, so several warps share each 32-lane quarter of tensor memory
-  static constexpr int kParts = FAM == FAM_W4A16 ? 4 : FAM == FAM_W8A16 ? 2 : 1;
+  static constexpr int kParts = FAM == FAM_W4A16 ? 2 : FAM == FAM_W8A16 ? 2 : 1;
   static constexpr int kHelperThreads = kHelpers ? 128 * kParts : 0;
   // the converter warps of the mixed kinds form two groups that take alternate stages (each owns one of the two widened
   // A buffers), so the waits and the store latency of one stage overlap the arithmetic of the next; within a group

@@ -36,7 +36,7 @@ def test_tc_info_table():
     for kind in L.KINDS:
         for cfg in range(10):
             bp, bq, threads, stage = L.tc_info(kind, cfg)
-            want = 704 if kind.startswith("w4a16") else 448 if kind.startswith("w8a16") else 320 if kind == "nvfp4" else 192
+            want = 448 if kind.startswith(("w4a16", "w8a16")) else 320 if kind == "nvfp4" else 192
             assert bp == 128 and bq == 16 << (cfg % 5) and threads == want
             assert stage % 1024 == 0 and (stage == 0) == (L.max_stages(kind, cfg) == 0)
         for cfg, width in zip(L.PAIR_CFGS, (128, 256)):  # 256-row tiles on CTA pairs: unconverted operands only
